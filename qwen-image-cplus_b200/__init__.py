@@ -1,0 +1,202 @@
+"""Host-side binding of libqipack_b200.so (include/qipack_b200.h) for Python callers.
+
+The product is the C-ABI shared library built from ``csrc/``; this module only loads it and
+mirrors the reference's thin operator wrappers (qwen_image_cuda/src/cuda.cplus:128-130:
+``w4a4_quantize_activations``, ``w4a4_gemm``, ``w4a16_gemm``, ``f32_to_f16``) and its
+dispatcher ``linear`` (qwen_image_cuda/src/transformer.cplus:673-713) with the same argument
+order and the same int status return (0 = success, 1 = cudaErrorInvalidValue).
+
+Pointers may be given as integers or as anything with ``data_ptr()`` (torch tensors).
+There is no CPU path: loading fails loudly when the library has not been built.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(_HERE)
+LIB_PATH = os.path.join(_HERE, "libqipack_b200.so")
+SOURCES = ["qipack_b200.cu", "ptx.cuh", "quantize.cuh", "w4a16_gemm.cuh", "w4a16_gemv.cuh", "w4a4_gemm.cuh",
+           "shard.cuh"]
+
+DTYPE_F32 = 0
+DTYPE_F16 = 1
+SCHEME_W4A16 = 5
+SCHEME_W4A4_H256 = 6
+CUDA_ERROR_INVALID_VALUE = 1
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-shared"]
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile csrc/ for sm_100a into libqipack_b200.so next to this file (nvcc cross-compiles
+    without a GPU)."""
+    sources = [os.path.join(_HERE, "csrc", name) for name in SOURCES]
+    sources = [s for s in sources if os.path.exists(s)] + [os.path.join(_ROOT, "include", "qipack_b200.h")]
+    stale = force or not os.path.exists(LIB_PATH) or any(
+        os.path.getmtime(s) > os.path.getmtime(LIB_PATH) for s in sources)
+    if stale:
+        nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+        command = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(_HERE, "csrc", "qipack_b200.cu")]
+        if verbose:
+            command.insert(1, "-Xptxas")
+            command.insert(2, "-v")
+        subprocess.run(command, check=True)
+    return LIB_PATH
+
+
+class qi_packed_linear(ctypes.Structure):
+    _fields_ = [("scheme", ctypes.c_uint32), ("group_size", ctypes.c_uint32), ("n", ctypes.c_int),
+                ("k", ctypes.c_int), ("weights", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+                ("zeros", ctypes.c_void_p), ("bias", ctypes.c_void_p)]
+
+
+class qi_linear_work(ctypes.Structure):
+    _fields_ = [("codes", ctypes.c_void_p), ("code_scales", ctypes.c_void_p), ("halves", ctypes.c_void_p)]
+
+
+_P, _I, _LL, _ULL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_ulonglong
+
+# name -> argument types; every entry point of include/qipack_b200.h
+SIGNATURES = {
+    "qi_w4a4_quantize_activations": [_P, _P, _P, _I, _I],
+    "qi_w4a4_gemm": [_P, _P, _P, _P, _P, _I, _I, _I],
+    "qi_w4a16_gemm": [_P, _P, _P, _P, _P, _I, _I, _I],
+    "qi_f32_to_f16": [_P, _P, _ULL],
+    "qi_w4a4_quantize_activations_ex": [_P, _I, _P, _P, _I, _I, _P],
+    "qi_w4a4_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
+    "qi_w4a16_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
+    "qi_w4a16_gemv_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
+    "qi_w4a16_dequantize_ex": [_P, _P, _P, _P, _I, _I, _P],
+    "qi_w4a4_group_dots_ex": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "qi_linear": [ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _I, _LL, _I, _I, _P],
+    "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
+    "qi_tune_w4a16_tile": [_I],
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library. Raises if it was never built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                               "(the packed-linear operators exist only as CUDA kernels)")
+        loaded = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in SIGNATURES.items():
+            function = getattr(loaded, name)
+            function.argtypes = argtypes
+            function.restype = ctypes.c_int
+        loaded.qi_b200_version.restype = ctypes.c_char_p
+        loaded.qi_b200_version.argtypes = []
+        _lib = loaded
+    return _lib
+
+
+def _p(pointer) -> ctypes.c_void_p:
+    if pointer is None:
+        return ctypes.c_void_p(0)
+    if hasattr(pointer, "data_ptr"):
+        return ctypes.c_void_p(pointer.data_ptr())
+    return ctypes.c_void_p(int(pointer))
+
+
+def version() -> str:
+    return lib().qi_b200_version().decode()
+
+
+# ---- the reference's operator wrappers (cuda.cplus:128-130), same argument order -------------
+
+def w4a4_quantize_activations(x, codes, scales, m: int, k: int) -> int:
+    return lib().qi_w4a4_quantize_activations(_p(x), _p(codes), _p(scales), m, k)
+
+
+def w4a4_gemm(a_codes, a_scales, w_codes, w_scales, y, m: int, n: int, k: int) -> int:
+    return lib().qi_w4a4_gemm(_p(a_codes), _p(a_scales), _p(w_codes), _p(w_scales), _p(y), m, n, k)
+
+
+def w4a16_gemm(x_half, codes, scales, minimums, y, m: int, n: int, k: int) -> int:
+    return lib().qi_w4a16_gemm(_p(x_half), _p(codes), _p(scales), _p(minimums), _p(y), m, n, k)
+
+
+def f32_to_f16(source, out, count: int) -> int:
+    return lib().qi_f32_to_f16(_p(source), _p(out), count)
+
+
+# ---- extended forms ------------------------------------------------------------------------------
+
+def w4a4_quantize_activations_ex(x, x_dtype: int, codes, scales, m: int, k: int, stream=None) -> int:
+    return lib().qi_w4a4_quantize_activations_ex(_p(x), x_dtype, _p(codes), _p(scales), m, k, _p(stream))
+
+
+def w4a4_gemm_ex(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,
+                 stream=None) -> int:
+    return lib().qi_w4a4_gemm_ex(_p(a_codes), _p(a_scales), _p(w_codes), _p(w_scales), _p(bias), _p(y), y_dtype,
+                                 ldy, m, n, k, _p(stream))
+
+
+def w4a16_gemm_ex(x_half, codes, scales, minimums, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,
+                  stream=None) -> int:
+    return lib().qi_w4a16_gemm_ex(_p(x_half), _p(codes), _p(scales), _p(minimums), _p(bias), _p(y), y_dtype, ldy,
+                                  m, n, k, _p(stream))
+
+
+def w4a16_gemv_ex(x_half, codes, scales, minimums, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,
+                  stream=None) -> int:
+    return lib().qi_w4a16_gemv_ex(_p(x_half), _p(codes), _p(scales), _p(minimums), _p(bias), _p(y), y_dtype, ldy,
+                                  m, n, k, _p(stream))
+
+
+def w4a16_dequantize_ex(codes, scales, minimums, w_half, n: int, k: int, stream=None) -> int:
+    return lib().qi_w4a16_dequantize_ex(_p(codes), _p(scales), _p(minimums), _p(w_half), n, k, _p(stream))
+
+
+def w4a4_group_dots_ex(a_codes, a_scales, w_codes, w_scales, y, dots, m: int, n: int, k: int, stream=None) -> int:
+    return lib().qi_w4a4_group_dots_ex(_p(a_codes), _p(a_scales), _p(w_codes), _p(w_scales), _p(y), _p(dots), m, n,
+                                       k, _p(stream))
+
+
+def kernel_status() -> int:
+    """Code of the first wait that gave up on the current device since the last call (0 = none)."""
+    value = ctypes.c_uint(0)
+    error = lib().qi_kernel_status(ctypes.byref(value))
+    if error != 0:
+        raise RuntimeError(f"qi_kernel_status: cuda status {error}")
+    return int(value.value)
+
+
+def tune_w4a16_tile(tile: int) -> int:
+    return lib().qi_tune_w4a16_tile(tile)
+
+
+# ---- transformer::linear (transformer.cplus:673-713) ------------------------------------------
+
+class PackedLinear:
+    """One packed record resident on the device: scheme, n, k and the three regions."""
+
+    def __init__(self, scheme: int, n: int, k: int, weights, scales, zeros=None, bias=None, group_size: int = 64):
+        self.scheme, self.n, self.k, self.group_size = scheme, n, k, group_size
+        self.weights, self.scales, self.zeros, self.bias = weights, scales, zeros, bias  # keep tensors alive
+        self.record = qi_packed_linear(scheme, group_size, n, k, _p(weights), _p(scales), _p(zeros), _p(bias))
+
+
+class LinearWork:
+    """The activation arena of transformer.cplus:649-651 (codes, code_scales, halves)."""
+
+    def __init__(self, codes, code_scales, halves):
+        self.codes, self.code_scales, self.halves = codes, code_scales, halves
+        self.work = qi_linear_work(_p(codes), _p(code_scales), _p(halves))
+
+
+def linear(model: PackedLinear, work: LinearWork, input, output, rows: int, reuse_input: bool = False, *,
+           input_dtype: int = DTYPE_F32, output_dtype: int = DTYPE_F32, ld_output: int | None = None,
+           stream=None) -> int:
+    """output[rows, n] = input[rows, k] . W^T for one packed record; 0 on success."""
+    return lib().qi_linear(ctypes.byref(model.record), ctypes.byref(work.work), _p(input), input_dtype, _p(output),
+                           output_dtype, model.n if ld_output is None else ld_output, rows, int(reuse_input),
+                           _p(stream))

@@ -1,0 +1,261 @@
+// Thin wrappers over the sm_100a PTX this library is built from: mbarriers, TMA
+// (cp.async.bulk.tensor, never multicast), tcgen05 (TMEM allocation, MMA, commit, load)
+// and the proxy / thread-sync fences between them. Every wait is bounded: a wait that
+// runs out records where it gave up in a status word and returns false, so that a logic
+// error ends in an error code and never in a hung device.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qi {
+
+// Status word written by a kernel that gave up on a wait (0 = healthy). The high half
+// says which wait, the low half carries block / stage detail.
+enum : uint32_t {
+    STATUS_OK = 0,
+    STATUS_WAIT_FULL = 0x00010000u,       // consumer waited for TMA data
+    STATUS_WAIT_EMPTY = 0x00020000u,      // producer waited for a free smem stage
+    STATUS_WAIT_READY = 0x00030000u,      // MMA warp waited for the unpacked operand
+    STATUS_WAIT_TMEM_FULL = 0x00040000u,  // epilogue waited for an accumulator
+    STATUS_WAIT_TMEM_EMPTY = 0x00050000u, // MMA warp waited for a drained accumulator
+    STATUS_BAD_ARGUMENT = 0x00060000u,
+};
+
+// Fast spins first, then 128 ns sleeps until two seconds of wall clock have passed.
+constexpr uint32_t WAIT_FAST_SPINS = 1u << 12;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *pointer) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    return now;
+}
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t predicate = 0;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(predicate));
+    return predicate != 0;
+}
+
+// ---- mbarrier ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void mbarrier_init(uint64_t *barrier, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(barrier)), "r"(count));
+}
+
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbarrier_arrive(uint64_t *barrier) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(barrier)) : "memory");
+}
+
+__device__ __forceinline__ void mbarrier_arrive_expect_tx(uint64_t *barrier, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(barrier)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbarrier_try_wait(uint64_t *barrier, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(barrier)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait. On time-out writes `code` to *status (first writer wins) and returns false;
+// also returns false as soon as another thread of the grid has recorded a failure.
+__device__ __forceinline__ bool mbarrier_wait(uint64_t *barrier, uint32_t parity, uint32_t *status,
+                                              uint32_t code) {
+    for (uint32_t spin = 0; spin < WAIT_FAST_SPINS; ++spin)
+        if (mbarrier_try_wait(barrier, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    while (true) {
+        if (mbarrier_try_wait(barrier, parity)) return true;
+        __nanosleep(128);
+        if (*reinterpret_cast<volatile uint32_t *>(status) != 0) return false;
+        if (global_timer_ns() - start > WAIT_LIMIT_NS) break;
+    }
+    atomicCAS(status, 0u, code);
+    return false;
+}
+
+// ---- TMA ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// 2-D tiled load global -> shared, completion on an mbarrier of this CTA. x is the
+// innermost (contiguous) coordinate in elements and must keep x * element size a multiple
+// of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void *smem, const CUtensorMap *map, uint64_t *barrier, int x,
+                                            int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(barrier)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Generic-proxy writes to shared memory become visible to the async proxy (TMA, tcgen05).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- tcgen05 -----------------------------------------------------------------------------
+
+// One whole warp allocates `columns` (power of two, >= 32) TMEM columns; the base address
+// lands in *slot (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)),
+                 "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// Arrives once on `barrier` when every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void tcgen05_commit(uint64_t *barrier) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(barrier))
+                 : "memory");
+}
+
+// Shared-memory operand descriptor for a K-major tile in the 128-byte-swizzled canonical
+// layout: rows of 128 bytes, 8-row groups 1024 bytes apart, 16-byte chunk c of row r stored
+// at chunk position c ^ (r % 8). `address` may point inside the first 128 bytes of a row
+// to step along K.
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t address) {
+    uint64_t descriptor = 0;
+    descriptor |= static_cast<uint64_t>((address & 0x3FFFFu) >> 4);  // start address, 16-byte units
+    descriptor |= static_cast<uint64_t>(1) << 16;                    // leading byte offset (unused when swizzled)
+    descriptor |= static_cast<uint64_t>(1024 >> 4) << 32;            // stride byte offset between 8-row groups
+    descriptor |= static_cast<uint64_t>(1) << 46;                    // descriptor version for sm_100
+    descriptor |= static_cast<uint64_t>(2) << 61;                    // layout type: 128-byte swizzle
+    return descriptor;
+}
+
+// Instruction descriptors: D format, A/B formats, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc_f16_f32(int m, int n) {
+    return (1u << 4) /* D = f32 */ | (0u << 7) /* A = f16 */ | (0u << 10) /* B = f16 */ |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__host__ __device__ constexpr uint32_t umma_idesc_s8_s32(int m, int n) {
+    return (2u << 4) /* D = s32 */ | (1u << 7) /* A = s8 */ | (1u << 10) /* B = s8 */ |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3_f32(int m, int n) {
+    return (1u << 4) /* D = f32 */ | (0u << 7) /* A = e4m3 */ | (0u << 10) /* B = e4m3 */ |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread. accumulate == 0 overwrites D.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// TMEM -> registers: this warp's 32 lanes x 32 consecutive 32-bit columns; thread t gets
+// lane (warp % 4) * 32 + t, register j gets column `address.column + j`.
+__device__ __forceinline__ void tmem_load_32x32(uint32_t address, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(address)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Warpgroup-wide register reallocation (all four warps of the warpgroup execute it).
+template <uint32_t REGISTERS>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGISTERS));
+}
+template <uint32_t REGISTERS>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGISTERS));
+}
+
+// ---- small utilities -----------------------------------------------------------------------
+
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+}  // namespace qi

@@ -1,0 +1,353 @@
+// C ABI of the library (include/qipack_b200.h): argument checks, tensor-map encoding, tile
+// selection and launches. One translation unit so that every kernel shares one status word.
+#include "../../include/qipack_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "quantize.cuh"
+#include "w4a16_gemm.cuh"
+#include "w4a16_gemv.cuh"
+#include "w4a4_gemm.cuh"
+
+namespace qi {
+namespace {
+
+constexpr int INVALID = static_cast<int>(cudaErrorInvalidValue);
+
+bool aligned16(const void *pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15) == 0; }
+
+// ---- per-device facts ------------------------------------------------------------------------
+
+constexpr int MAX_DEVICES = 64;
+
+int current_device() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return -1;
+    return device;
+}
+
+int sm_count(int device) {
+    static int cached[MAX_DEVICES];
+    if (cached[device] == 0) {
+        int count = 0;
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+            return 148;
+        cached[device] = count;
+    }
+    return cached[device];
+}
+
+// ---- TMA descriptors ---------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled function = nullptr;
+    if (function == nullptr) {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            function = reinterpret_cast<EncodeTiled>(entry);
+    }
+    return function;
+}
+
+// A row-major [rows, row_bytes / element] matrix seen as a 2-D tensor; box = box_inner elements
+// x box_rows rows. Out-of-range rows read as zero.
+bool make_map(CUtensorMap *map, CUtensorMapDataType type, int element_bytes, const void *base, uint64_t inner,
+              uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows,
+              CUtensorMapSwizzle swizzle) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    (void)element_bytes;
+    return encode(map, type, 2, const_cast<void *>(base), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// ---- tile selection -----------------------------------------------------------------------------
+
+// 0 = choose by shape; otherwise forces one W4A16 tile: 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256.
+int g_w4a16_tile = 0;
+
+template <int NUM_M, int BN, int STAGES>
+int launch_w4a16(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
+                 void *y, const GemmShape &shape, cudaStream_t stream, int device) {
+    using T = w4a16::Tile<NUM_M, BN, STAGES>;
+    CUtensorMap map_x, map_codes;
+    if (!make_map(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_half, shape.k, shape.m,
+                  static_cast<uint64_t>(shape.k) * 2, 64, T::BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return INVALID;
+    if (!make_map(&map_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, shape.k / 2, shape.n,
+                  static_cast<uint64_t>(shape.k) / 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return INVALID;
+    auto kernel = w4a16::gemm_kernel<NUM_M, BN, STAGES>;
+    static bool configured[MAX_DEVICES];
+    if (!configured[device]) {
+        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (error != cudaSuccess) return static_cast<int>(error);
+        configured[device] = true;
+    }
+    const int tiles = ((shape.m + T::BM - 1) / T::BM) * ((shape.n + BN - 1) / BN);
+    const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+    kernel<<<grid, w4a16::THREADS, T::SMEM_BYTES, stream>>>(map_x, map_codes, static_cast<const __half *>(scales),
+                                                            static_cast<const __half *>(minimums), bias, y, shape);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN, int STAGES>
+int launch_w4a4(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
+                const float *bias, void *y, int32_t *dots, const GemmShape &shape, cudaStream_t stream, int device) {
+    using T = w4a4::Tile<BN, STAGES>;
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, shape.k / 2, shape.m,
+                  static_cast<uint64_t>(shape.k) / 2, 64, T::BM, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return INVALID;
+    if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_codes, shape.k / 2, shape.n,
+                  static_cast<uint64_t>(shape.k) / 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return INVALID;
+    auto kernel = dots != nullptr ? w4a4::gemm_kernel<BN, STAGES, true> : w4a4::gemm_kernel<BN, STAGES, false>;
+    static bool configured[MAX_DEVICES][2];
+    if (!configured[device][dots != nullptr]) {
+        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (error != cudaSuccess) return static_cast<int>(error);
+        configured[device][dots != nullptr] = true;
+    }
+    const int tiles = ((shape.m + T::BM - 1) / T::BM) * ((shape.n + BN - 1) / BN);
+    const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+    kernel<<<grid, w4a4::THREADS, T::SMEM_BYTES, stream>>>(map_a, map_w, static_cast<const __half *>(a_scales),
+                                                           static_cast<const __half *>(w_scales), bias, y, dots, shape);
+    return static_cast<int>(cudaGetLastError());
+}
+
+bool output_ok(const void *y, int y_dtype, long long ldy, int n) {
+    if (y == nullptr || !aligned16(y) || ldy < n) return false;
+    if (y_dtype == QI_DTYPE_F32) return ldy % 4 == 0;
+    if (y_dtype == QI_DTYPE_F16) return ldy % 8 == 0;
+    return false;
+}
+
+__global__ void dequantize_kernel(const uint8_t *__restrict__ codes, const __half *__restrict__ scales,
+                                  const __half *__restrict__ minimums, __half *__restrict__ out, int n, int k) {
+    // one thread per 16 code bytes (32 inputs, half a group)
+    const long long chunks = static_cast<long long>(n) * (k / 32);
+    const long long chunk = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (chunk >= chunks) return;
+    const long long row = chunk / (k / 32);
+    const int in_row = static_cast<int>(chunk % (k / 32));
+    const int group = in_row / 2;
+    const uint4 packed = __ldg(reinterpret_cast<const uint4 *>(codes + row * (k / 2)) + in_row);
+    const __half2 scale2 = __half2half2(__ldg(scales + row * (k / 64) + group));
+    const __half2 minimum2 = __half2half2(__ldg(minimums + row * (k / 64) + group));
+    uint4 values[4];
+    w4a16::unpack32(packed, scale2, minimum2, values);
+    uint4 *destination = reinterpret_cast<uint4 *>(out + row * k + in_row * 32);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) destination[j] = values[j];
+}
+
+int w4a16_gemv(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
+               void *y, int y_dtype, long long ldy, int m, int n, int k, cudaStream_t stream) {
+    if (m < 1 || m > 8 || n <= 0 || k <= 0 || n % 16 != 0 || k % 64 != 0) return INVALID;
+    if (!x_half || !codes || !scales || !minimums || !y) return INVALID;
+    if (!aligned16(x_half) || !aligned16(codes) || (k % 8) != 0) return INVALID;
+    if (ldy < n || (y_dtype != QI_DTYPE_F32 && y_dtype != QI_DTYPE_F16)) return INVALID;
+    const int quads = (k / 64 + 3) / 4;
+    int k_splits = 1;
+    for (int candidate = 8; candidate >= 1; candidate /= 2)
+        if (quads % candidate == 0) { k_splits = candidate; break; }
+    const int row_tiles = w4a16::GEMV_WARPS / k_splits;
+    const int blocks = (n / 16 + row_tiles - 1) / row_tiles;
+    w4a16::gemv_kernel<<<blocks, w4a16::GEMV_THREADS, 0, stream>>>(
+        static_cast<const __half *>(x_half), static_cast<const uint8_t *>(codes), static_cast<const __half *>(scales),
+        static_cast<const __half *>(minimums), bias, y, m, n, k, ldy, y_dtype == QI_DTYPE_F16, k_splits);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
+               void *y, int y_dtype, long long ldy, int m, int n, int k, cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 64 != 0) return INVALID;
+    if (!x_half || !codes || !scales || !minimums) return INVALID;
+    if (!aligned16(x_half) || !aligned16(codes) || !output_ok(y, y_dtype, ldy, n)) return INVALID;
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
+    int tile = g_w4a16_tile;
+    if (tile == 0) {
+        // tall tiles halve the unpacking work per MMA; take them when they still fill the machine
+        const int sms = sm_count(device);
+        const long long tiles_256 = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
+        const long long tiles_256x128 = static_cast<long long>((m + 255) / 256) * ((n + 127) / 128);
+        if (m > 128 && tiles_256 >= 2LL * sms) tile = 4;
+        else if (m > 128 && tiles_256x128 >= sms) tile = 2;
+        else tile = 1;
+    }
+    switch (tile) {
+        case 1: return launch_w4a16<1, 128, 6>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
+        case 2: return launch_w4a16<2, 128, 4>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
+        case 3: return launch_w4a16<1, 256, 4>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
+        case 4: return launch_w4a16<2, 256, 3>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
+        default: return INVALID;
+    }
+}
+
+int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales, const float *bias,
+              void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n, int k, cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 128 != 0) return INVALID;
+    if (!a_codes || !a_scales || !w_codes || !w_scales) return INVALID;
+    if (!aligned16(a_codes) || !aligned16(w_codes) || (reinterpret_cast<uintptr_t>(a_scales) & 3) ||
+        (reinterpret_cast<uintptr_t>(w_scales) & 3) || !output_ok(y, y_dtype, ldy, n))
+        return INVALID;
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
+    return launch_w4a4<128, 4>(a_codes, a_scales, w_codes, w_scales, bias, y, dots, shape, stream, device);
+}
+
+}  // namespace
+}  // namespace qi
+
+using namespace qi;
+
+extern "C" {
+
+int qi_w4a4_quantize_activations_ex(const void *x, int x_dtype, void *codes, void *scales, int m, int k, void *stream) {
+    if (m < 0 || k <= 0 || k % 256 != 0) return INVALID;
+    if (x_dtype != QI_DTYPE_F32 && x_dtype != QI_DTYPE_F16) return INVALID;
+    if (m == 0) return 0;
+    if (!x || !codes || !scales || !aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 7) ||
+        (reinterpret_cast<uintptr_t>(scales) & 1))
+        return INVALID;
+    return static_cast<int>(launch_quantize_activations(x, x_dtype == QI_DTYPE_F16, codes, scales, m, k,
+                                                        static_cast<cudaStream_t>(stream)));
+}
+
+int qi_w4a4_quantize_activations(const float *x, void *codes, void *scales, int m, int k) {
+    return qi_w4a4_quantize_activations_ex(x, QI_DTYPE_F32, codes, scales, m, k, nullptr);
+}
+
+int qi_w4a4_gemm_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
+                    const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
+    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales, float *y,
+                 int m, int n, int k) {
+    if (m % 128 != 0 || n % 128 != 0 || k % 256 != 0) return INVALID;  // gemm.cu:185
+    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, nullptr, y, QI_DTYPE_F32, n, nullptr, m, n, k, nullptr);
+}
+
+int qi_w4a4_group_dots_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
+                          float *y, int32_t *dots, int m, int n, int k, void *stream) {
+    if (dots == nullptr) return INVALID;
+    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, nullptr, y, QI_DTYPE_F32, n, dots, m, n, k,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a16_gemv_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
+                     const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
+    return w4a16_gemv(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a16_gemm_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
+                     const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
+    if (m >= 1 && m <= 8 && n % 16 == 0)
+        return w4a16_gemv(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, static_cast<cudaStream_t>(stream));
+    return w4a16_gemm(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a16_gemm(const void *x_half, const void *codes, const void *scales, const void *minimums, float *y, int m,
+                  int n, int k) {
+    if (m % 128 != 0 || n % 128 != 0 || k % 64 != 0) return INVALID;  // gemm.cu:264
+    return w4a16_gemm(x_half, codes, scales, minimums, nullptr, y, QI_DTYPE_F32, n, m, n, k, nullptr);
+}
+
+int qi_f32_to_f16(const float *source, void *out, unsigned long long count) {
+    if (count == 0) return 0;
+    if (!source || !out) return INVALID;
+    return static_cast<int>(launch_f32_to_f16(source, out, count, nullptr));
+}
+
+int qi_w4a16_dequantize_ex(const void *codes, const void *scales, const void *minimums, void *w_half, int n, int k,
+                           void *stream) {
+    if (n <= 0 || k <= 0 || k % 64 != 0) return INVALID;
+    if (!codes || !scales || !minimums || !w_half || !aligned16(codes) || !aligned16(w_half)) return INVALID;
+    const long long chunks = static_cast<long long>(n) * (k / 32);
+    const long long blocks = (chunks + 255) / 256;
+    if (blocks > 0x7fffffffLL) return INVALID;
+    dequantize_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(codes), static_cast<const __half *>(scales), static_cast<const __half *>(minimums),
+        static_cast<__half *>(w_half), n, k);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int qi_linear(const qi_packed_linear *record, const qi_linear_work *work, const void *input, int input_dtype,
+              void *output, int output_dtype, long long ld_output, int rows, int reuse_input, void *stream) {
+    if (!record || !work || !input || !output || rows <= 0) return INVALID;
+    if (record->group_size != 64) return INVALID;
+    if (input_dtype != QI_DTYPE_F32 && input_dtype != QI_DTYPE_F16) return INVALID;
+    const int n = record->n, k = record->k;
+    if (record->scheme == QI_SCHEME_W4A4_H256) {  // transformer.cplus:702-708
+        if (!work->codes || !work->code_scales) return INVALID;
+        if (!reuse_input) {
+            const int status = qi_w4a4_quantize_activations_ex(input, input_dtype, work->codes, work->code_scales, rows, k, stream);
+            if (status != 0) return status;
+        }
+        return qi_w4a4_gemm_ex(work->codes, work->code_scales, record->weights, record->scales, record->bias, output,
+                               output_dtype, ld_output, rows, n, k, stream);
+    }
+    if (record->scheme == QI_SCHEME_W4A16) {  // transformer.cplus:709-712
+        const void *x_half = input;
+        if (input_dtype == QI_DTYPE_F32) {
+            if (!work->halves) return INVALID;
+            if (!reuse_input) {
+                const int status = static_cast<int>(launch_f32_to_f16(static_cast<const float *>(input), work->halves,
+                                                                      static_cast<unsigned long long>(rows) * k,
+                                                                      static_cast<cudaStream_t>(stream)));
+                if (status != 0) return status;
+            }
+            x_half = work->halves;
+        }
+        return qi_w4a16_gemm_ex(x_half, record->weights, record->scales, record->zeros, record->bias, output,
+                                output_dtype, ld_output, rows, n, k, stream);
+    }
+    return INVALID;
+}
+
+int qi_kernel_status(unsigned int *status) {
+    if (!status) return INVALID;
+    cudaError_t error = cudaDeviceSynchronize();
+    if (error != cudaSuccess) return static_cast<int>(error);
+    uint32_t value = 0;
+    error = cudaMemcpyFromSymbol(&value, g_status, sizeof(value));
+    if (error != cudaSuccess) return static_cast<int>(error);
+    if (value != 0) {
+        const uint32_t zero = 0;
+        error = cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
+    }
+    *status = value;
+    return static_cast<int>(error);
+}
+
+// Forces one W4A16 tile (1..4) or returns to the shape heuristic (0). For tuning runs.
+int qi_tune_w4a16_tile(int tile) {
+    if (tile < 0 || tile > 4) return INVALID;
+    g_w4a16_tile = tile;
+    return 0;
+}
+
+const char *qi_b200_version(void) { return "qipack_b200 0.1 sm_100a"; }
+
+}  // extern "C"
