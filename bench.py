@@ -1,0 +1,386 @@
+#!/usr/bin/env python3
+"""Benchmark of the QIPACK v6 packed-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = one pass over the four linears of one Qwen-Image MMDiT block image stream at
+1024x1024 under W4A4 (H256, g64): M = 4096 image tokens, hidden 3072 —
+fused q/k/v 3072->9216, attention out 3072->3072, MLP fc1 3072->12288, fc2 12288->3072 —
+each with its own activation rotation + quantisation (fp16 in) and fp16 outputs.
+2*M*N*K summed over the four linears = 927.7 G operations per step.
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): every linear's packed weights are
+sharded by output columns, rank r computes y[:, r*N/R:(r+1)*N/R] and the slices are
+all-gathered over NVLink; total work is fixed (strong scaling).
+
+Prints ONE JSON line. `value` is device-timed with inputs resident in HBM; `e2e` is the same
+metric through the C ABI with host buffers (pinned) copied in and results copied out every step;
+`roofline` is the W4A4 GEMM kernel's achieved rate from CUDA events around its launches inside
+the timed region; `cpu_baseline` is the CPU oracle port timed on this host on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_TOKENS = 4096
+HIDDEN = 3072
+# name, n, k, kind of activation
+LINEARS = [("qkv", 9216, 3072, "outliers"), ("attn_out", 3072, 3072, "outliers"),
+           ("fc1", 12288, 3072, "outliers"), ("fc2", 3072, 12288, "gelu")]
+OPS_PER_STEP = sum(2.0 * M_TOKENS * n * k for _, n, k, _ in LINEARS)
+METRIC = "packed W4A4/W4A16 GEMM TOPS at M=4096 block shapes, % of tensor/HBM roofline"
+UNIT = "TOPS"
+WORKLOAD = "qwen-image MMDiT block image stream, W4A4 H256 g64, M=4096 hidden=3072: qkv 3072->9216, out 3072->3072, fc1 3072->12288, fc2 12288->3072"
+CPU_SAMPLE_ROWS = 256
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            data = json.load(handle)
+        return {"hbm_gbs": data["hbm_gbs"], "bf16_burst": data["bf16_tflops"],
+                "bf16_sustained": data["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# ---- clocks ------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.process, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            time.sleep(0.25)
+            self.process.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                maxima.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxima), "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ---- synthetic data (torch, on the device; not the hot path) ------------------------------------
+
+def hadamard_matrix(torch, device):
+    """The 256x256 matrix of the radix-4 butterfly (strides 1, 4, 16, 64): rotation = x @ H.T per chunk."""
+    h4 = 0.5 * torch.tensor([[1, 1, 1, -1], [1, 1, -1, 1], [1, -1, 1, 1], [-1, 1, 1, 1]], dtype=torch.float64)
+    h = torch.ones(1, 1, dtype=torch.float64)
+    for _ in range(4):
+        h = torch.kron(h4, h)  # the later pass (larger stride) is the outer factor
+    return h.to(device=device, dtype=torch.float32)
+
+
+def make_packed_w4a4(torch, generator, n, k, device):
+    """W ~ N(0, 0.02) rounded to fp16, rotated by H256 per 256-chunk and quantised per 64-group to
+    signed 4-bit codes with scale fp16(max|w'|/7) (int4_pack.cplus:322-363 without the clip search,
+    which changes values, not timing). Returns codes [n, k/2] uint8, scales [n, k/64] fp16."""
+    w = (torch.randn(n, k, generator=generator, device=device) * 0.02).half().float()
+    h = hadamard_matrix(torch, device)
+    rotated = (w.view(n, k // 256, 256) @ h.t()).view(n, k // 64, 64)
+    peak = rotated.abs().amax(dim=-1)
+    scale = torch.clamp(peak / 7.0, min=2.0 ** -24).half()
+    codes = torch.clamp(torch.round(rotated / scale.float().unsqueeze(-1)), -7, 7).to(torch.int16).view(n, k) & 0xF
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).to(torch.uint8).contiguous()
+    return packed, scale.contiguous()
+
+
+def make_activations(torch, generator, m, k, kind, device):
+    x = torch.randn(m, k, generator=generator, device=device)
+    if kind == "outliers":
+        channels = torch.randperm(k, generator=generator, device=device)[: max(1, k // 100)]
+        x[:, channels] *= 20.0
+    elif kind == "gelu":
+        x = torch.nn.functional.gelu(x, approximate="tanh")
+    return x.half().contiguous()
+
+
+# ---- the b200 arm ---------------------------------------------------------------------------------
+
+def run_b200(args):
+    import torch
+    import __graft_entry__ as entry
+
+    qi = entry.load_package()
+    qi.lib()  # no fallback: the kernels are the product
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch N > 1 with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_module
+        dist = dist_module
+        dist.init_process_group("nccl", device_id=device)
+
+    generator = torch.Generator(device=device)
+    generator.manual_seed(1234)  # same weights and activations on every rank
+    stream = torch.cuda.Stream(device=device)
+    stream_handle = stream.cuda_stream
+    m = M_TOKENS
+    layers = []
+    for name, n, k, kind in LINEARS:
+        w_codes, w_scales = make_packed_w4a4(torch, generator, n, k, device)
+        x = make_activations(torch, generator, m, k, kind, device)
+        n_local = n // world
+        lo = rank * n_local
+        layer = {
+            "name": name, "n": n, "k": k, "n_local": n_local, "x": x,
+            "w_codes": w_codes[lo:lo + n_local].contiguous(), "w_scales": w_scales[lo:lo + n_local].contiguous(),
+            "a_codes": torch.empty(m, k // 2, dtype=torch.uint8, device=device),
+            "a_scales": torch.empty(m, k // 64, dtype=torch.float16, device=device),
+            "y_local": torch.empty(m, n_local, dtype=torch.float16, device=device),
+            "y_all": torch.empty(world, m, n_local, dtype=torch.float16, device=device) if world > 1 else None,
+        }
+        del w_codes, w_scales
+        layers.append(layer)
+    torch.cuda.synchronize()
+
+    launches = {"count": 0}
+
+    def step(record_gemm_events=None):
+        for layer in layers:
+            k, n_local = layer["k"], layer["n_local"]
+            status = qi.w4a4_quantize_activations_ex(layer["x"], qi.DTYPE_F16, layer["a_codes"], layer["a_scales"],
+                                                     m, k, stream_handle)
+            assert status == 0, f"quantise {layer['name']}: cuda status {status}"
+            if record_gemm_events is not None:
+                start = torch.cuda.Event(enable_timing=True)
+                start.record(stream)
+            status = qi.w4a4_gemm_ex(layer["a_codes"], layer["a_scales"], layer["w_codes"], layer["w_scales"], None,
+                                     layer["y_local"], qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
+            assert status == 0, f"gemm {layer['name']}: cuda status {status}"
+            if record_gemm_events is not None:
+                stop = torch.cuda.Event(enable_timing=True)
+                stop.record(stream)
+                record_gemm_events.append((start, stop, layer))
+            launches["count"] += 2
+            if dist is not None:
+                with torch.cuda.stream(stream):
+                    dist.all_gather_into_tensor(layer["y_all"].view(-1), layer["y_local"].view(-1))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    assert qi.kernel_status() == 0, "a kernel gave up on a wait during warm-up"
+
+    # ---- device-timed region: exactly `steps` steps
+    launches["count"] = 0
+    gemm_events = []
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        barrier()
+        begin.record(stream)
+        for _ in range(args.steps):
+            step(gemm_events)
+        end.record(stream)
+        barrier()
+    elapsed_ms = begin.elapsed_time(end)
+    timed_launches = launches["count"]
+    assert qi.kernel_status() == 0, "a kernel gave up on a wait during the timed region"
+    gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events)
+    gemm_ops = sum(2.0 * m * layer["n_local"] * layer["k"] for _, _, layer in gemm_events)
+
+    # ---- end to end: host buffers in, host buffers out, every step
+    host_x = [layer["x"].cpu().pin_memory() for layer in layers]
+    host_y = [torch.empty(m, layer["n_local"], dtype=torch.float16).pin_memory() for layer in layers]
+    h2d = sum(t.numel() * t.element_size() for t in host_x)
+    d2h = sum(t.numel() * t.element_size() for t in host_y)
+
+    def e2e_step():
+        with torch.cuda.stream(stream):
+            for layer, hx in zip(layers, host_x):
+                layer["x"].copy_(hx, non_blocking=True)
+        step()
+        with torch.cuda.stream(stream):
+            for layer, hy in zip(layers, host_y):
+                hy.copy_(layer["y_local"], non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_begin, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_begin.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_end.record(stream)
+    barrier()
+    e2e_ms = e2e_begin.elapsed_time(e2e_end)
+
+    times = torch.tensor([elapsed_ms, e2e_ms, gemm_ms], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, gemm_ms = (float(v) for v in times.tolist())
+
+    result = None
+    if rank == 0:
+        peaks = measured_peaks()
+        value = OPS_PER_STEP * args.steps / (elapsed_ms * 1e-3) / 1e12
+        e2e_value = OPS_PER_STEP * e2e_steps / (e2e_ms * 1e-3) / 1e12
+        # one GPU's GEMM launches: operations of its column slices over the time of its launches
+        achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12
+        int8_peak = 2.0 * peaks["bf16_sustained"]
+        working_set = sum(l["w_codes"].numel() + l["x"].numel() * 2 + l["a_codes"].numel() + l["y_local"].numel() * 2
+                          for l in layers)
+        result = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int4 codes, int8 tensor-core dots, fp32 fold",
+            "data": "synthetic: W ~ N(0,0.02) rotated (H256) and quantised to int4 g64 on the device, "
+                    "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
+            "config": {"workload": WORKLOAD, "m": m, "ops_per_step": OPS_PER_STEP,
+                       "parallelism": "single GPU" if world == 1 else f"N-sharded x{world} + all-gather",
+                       "outputs": "fp16", "l2": f"per-step working set {working_set / 1e6:.0f} MB per GPU exceeds the 126 MB L2"},
+            "gpu_launches": timed_launches,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "roofline": {"kernel": "w4a4 gemm_kernel", "bound": "tensor", "achieved": achieved, "peak": int8_peak,
+                         "unit": "TOP/s", "frac": achieved / int8_peak, "traffic": None,
+                         "peak_source": f"2 x the sustained bf16 figure of MEASURED_PEAKS.json ({peaks['source']}); "
+                                        "no int8 figure is measured, int8 runs at twice the bf16 rate",
+                         "launches_timed": len(gemm_events), "avg_launch_ms": gemm_ms / max(1, len(gemm_events))},
+            "clocks": sampler.summary(),
+        }
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
+# ---- the CPU arm: the oracle port on this host's cores ----------------------------------------------
+
+def cpu_port(rows: int, repeats: int, warmup: int):
+    """Times the CPU restatement of the same four linears (oracle/qipack_oracle.c, threaded over all
+    host cores) on the first `rows` activation rows. Returns (TOPS, cores, seconds per pass)."""
+    import numpy as np
+    from oracle import qipack_oracle as qo
+
+    rng = np.random.default_rng(1234)
+    cores = qo.max_threads()
+    work = []
+    for _, n, k, _ in LINEARS:
+        values = rng.integers(-7, 8, size=(n, k), dtype=np.int8).astype(np.int16) & 0xF
+        codes = (values[:, 0::2] | (values[:, 1::2] << 4)).astype(np.uint8)
+        scales = rng.uniform(1e-3, 6e-3, size=(n, k // 64)).astype(np.float16).view(np.uint16)
+        x = rng.standard_normal((rows, k), dtype=np.float32).astype(np.float16)
+        work.append((x, codes, scales))
+    for _ in range(warmup):
+        for x, codes, scales in work[:1]:
+            qo.w4a4_linear_fast(x, codes, scales, threads=cores)
+    start = time.perf_counter()
+    for _ in range(repeats):
+        for x, codes, scales in work:
+            qo.w4a4_linear_fast(x, codes, scales, threads=cores)
+    seconds = (time.perf_counter() - start) / repeats
+    ops = sum(2.0 * rows * n * k for _, n, k, _ in LINEARS)
+    return ops / seconds / 1e12, cores, seconds
+
+
+def run_reference(args):
+    """The reference's path on the host cores. The reference engine has no CPU implementation of
+    these linears and its NumPy evaluator cannot travel, so this is the C port of the same
+    arithmetic (kind "port"); each step is the block's four linears on a bounded row sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    steps = max(1, min(args.steps, 3))
+    tops, cores, seconds = cpu_port(CPU_SAMPLE_ROWS, steps, min(args.warmup, 1))
+    sample = f"first {CPU_SAMPLE_ROWS} of {M_TOKENS} rows of each of the four linears, activation quantisation included"
+    return {
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int4 codes, int32 dots, fp32 fold", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": CPU_SAMPLE_ROWS, "sample": sample},
+        "cpu_baseline": {"value": tops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        result = run_reference(args)
+        if result is not None:
+            print(json.dumps(result), flush=True)
+        return
+    result = run_b200(args)
+    if result is None:
+        return
+    if not args.no_cpu_baseline and result["n_gpus"] == 1:
+        tops, cores, seconds = cpu_port(CPU_SAMPLE_ROWS, 1, 1)
+        result["cpu_baseline"] = {
+            "value": tops, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"first {CPU_SAMPLE_ROWS} of {M_TOKENS} rows of each of the four linears "
+                      f"({seconds:.1f} s of CPU work), activation quantisation included"}
+    print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -75,6 +75,7 @@ SIGNATURES = {
     "qi_linear": [ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _I, _LL, _I, _I, _P],
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
     "qi_tune_w4a16_tile": [_I],
+    "qi_tune_ablate": [_I],
 }
 
 _lib = None
@@ -172,6 +173,10 @@ def kernel_status() -> int:
 
 def tune_w4a16_tile(tile: int) -> int:
     return lib().qi_tune_w4a16_tile(tile)
+
+
+def tune_ablate(flags: int) -> int:
+    return lib().qi_tune_ablate(flags)
 
 
 # ---- transformer::linear (transformer.cplus:673-713) ------------------------------------------

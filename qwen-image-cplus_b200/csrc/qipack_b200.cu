@@ -80,6 +80,7 @@ bool make_map(CUtensorMap *map, CUtensorMapDataType type, int element_bytes, con
 
 // 0 = choose by shape; otherwise forces one W4A16 tile: 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256.
 int g_w4a16_tile = 0;
+int g_ablate = 0;  // tuning only, see GemmShape::ablate
 
 template <int NUM_M, int BN, int STAGES>
 int launch_w4a16(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
@@ -182,7 +183,7 @@ int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const 
     if (!aligned16(x_half) || !aligned16(codes) || !output_ok(y, y_dtype, ldy, n)) return INVALID;
     const int device = current_device();
     if (device < 0) return INVALID;
-    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
     int tile = g_w4a16_tile;
     if (tile == 0) {
         // tall tiles halve the unpacking work per MMA; take them when they still fill the machine
@@ -211,7 +212,7 @@ int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, co
         return INVALID;
     const int device = current_device();
     if (device < 0) return INVALID;
-    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
     return launch_w4a4<128, 4>(a_codes, a_scales, w_codes, w_scales, bias, y, dots, shape, stream, device);
 }
 
@@ -345,6 +346,12 @@ int qi_kernel_status(unsigned int *status) {
 int qi_tune_w4a16_tile(int tile) {
     if (tile < 0 || tile > 4) return INVALID;
     g_w4a16_tile = tile;
+    return 0;
+}
+
+// Tuning only: switches parts of the GEMM kernels off to see what bounds them (results are then wrong).
+int qi_tune_ablate(int flags) {
+    g_ablate = flags;
     return 0;
 }
 
