@@ -98,6 +98,30 @@ int qi_w4a16_dequantize_ex(const void *codes, const void *scales, const void *mi
 int qi_w4a4_group_dots_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
                           float *y, int32_t *dots, int m, int n, int k, void *stream);
 
+/* ---- W4A4 with one byte per code (the fast path on B200) ------------------------------------ */
+/* tcgen05 has no 4-bit integer MMA. Codes -7..7 stored one per byte as FP8 E4M3 numbers (exact)
+ * go to the tensor cores as they are, and their fp32-accumulated group dots are exact integers
+ * (|dot| <= 3136). Weights are widened once when the pack is loaded (qi_w4a4_widen_codes_ex: same
+ * integers, twice the bytes of the packed codes); activations come out of the quantiser in this
+ * form directly. Scales are the pack's own. Results are the same bits as qi_w4a4_gemm's.
+ * None of these has a counterpart in the reference, whose int4 tensor-core path (gemm.cu:60-63)
+ * does not exist on this architecture. */
+
+/* codes [rows, k/2] packed nibbles -> bytes [rows, k]; k % 32 == 0. */
+int qi_w4a4_widen_codes_ex(const void *codes, void *bytes, long long rows, int k, void *stream);
+
+/* As qi_w4a4_quantize_activations_ex, also writing bytes [m, k]; codes may be NULL. */
+int qi_w4a4_quantize_activations_wide_ex(const void *x, int x_dtype, void *codes, void *scales, void *bytes, int m,
+                                         int k, void *stream);
+
+/* As qi_w4a4_gemm_ex on byte operands a_bytes [m, k], w_bytes [n, k]; k % 128 == 0. */
+int qi_w4a4_gemm_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                         const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
+
+/* As qi_w4a4_group_dots_ex, from the byte-operand kernel. */
+int qi_w4a4_group_dots_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                               float *y, int32_t *dots, int m, int n, int k, void *stream);
+
 /* ---- the dispatcher of transformer::linear (transformer.cplus:673-713) -------------------- */
 
 /* One packed record as the engine sees it after upload (int4_pack.cplus:76-95: scheme,
@@ -110,6 +134,7 @@ typedef struct qi_packed_linear {
     const void *scales;   /* [n, k/64] fp16 */
     const void *zeros;    /* minimums [n, k/64] fp16; NULL for scheme 6 */
     const float *bias;    /* [n] or NULL (the reference has none) */
+    const void *weights_wide; /* scheme 6 only, optional: qi_w4a4_widen_codes_ex(weights) [n, k] bytes */
 } qi_packed_linear;
 
 /* The activation arena of transformer.cplus:649-651: codes rows*k_max/2 bytes, code_scales
@@ -118,6 +143,7 @@ typedef struct qi_linear_work {
     void *codes;
     void *code_scales;
     void *halves;
+    void *wide;           /* optional: rows*k_max bytes; with weights_wide selects the byte-operand W4A4 path */
 } qi_linear_work;
 
 /* output[rows, n] = input[rows, k] . W^T for one record. `input` is float32 (the engine's
@@ -128,12 +154,48 @@ typedef struct qi_linear_work {
 int qi_linear(const qi_packed_linear *record, const qi_linear_work *work, const void *input, int input_dtype,
               void *output, int output_dtype, long long ld_output, int rows, int reuse_input, void *stream);
 
+/* ---- column (N) sharding over the GPUs of one box ------------------------------------------- */
+/* No counterpart in the reference, which drives one GPU (qwen_image_cuda/cuda/runtime.cu:6-19).
+ * One process per GPU. Rank r of R holds weight rows [r*N/R, (r+1)*N/R) of every region (codes,
+ * scales, minimums are per output row, so a shard is a contiguous slice of each), computes
+ * y[:, r*N/R:(r+1)*N/R] with the kernels above and the slices are all-gathered with NCCL over
+ * NVLink. NCCL is looked up at run time (dlopen of libnccl.so.2, or the path in QI_NCCL_LIBRARY),
+ * never linked. Errors of NCCL come back as 10000 + ncclResult_t, a missing NCCL as 10100. */
+
+#define QI_SHARD_ID_BYTES 128
+
+/* Host-only: the rows rank owns. Every shard must be a legal GEMM, so n % (ranks*128) == 0. */
+int qi_shard_plan(int n, int ranks, int rank, int *first_row, int *row_count);
+
+/* Rank 0 makes the 128-byte id; the caller carries it to the other ranks by any host channel. */
+int qi_shard_unique_id(void *id);
+
+/* Collective over all ranks; the current device becomes the rank's device. */
+int qi_shard_create(void **context, int rank, int ranks, const void *id);
+int qi_shard_destroy(void *context);
+int qi_shard_rank(void *context, int *rank, int *ranks);
+
+/* y_slabs [ranks][rows][n_local] <- every rank's y_local [rows][n_local], on `stream`. */
+int qi_shard_all_gather(void *context, const void *y_local, void *y_slabs, int output_dtype, int rows, int n_local,
+                        void *stream);
+
+/* qi_linear on this rank's shard (local_record->n = N/R rows) into y_local [rows, N/R], then the
+ * all-gather into y_slabs (skipped when y_slabs is NULL or there is one rank). */
+int qi_shard_linear(void *context, const qi_packed_linear *local_record, const qi_linear_work *work,
+                    const void *input, int input_dtype, void *y_local, void *y_slabs, int output_dtype, int rows,
+                    int reuse_input, void *stream);
+
 /* ---- diagnostics --------------------------------------------------------------------------- */
 
 /* Kernels of this library never spin without a bound: a wait that runs out records a code
  * (which wait, which stage) and the kernel returns. This reads and clears the code of the
  * current device (0 = healthy). Synchronises the device. */
 int qi_kernel_status(unsigned int *status);
+
+/* Tuning hooks (not for production): force one W4A16 tile shape (1..4, 0 = by shape); switch
+ * parts of the GEMM kernels off to see what bounds them (results are then wrong). */
+int qi_tune_w4a16_tile(int tile);
+int qi_tune_ablate(int flags);
 
 /* "qipack_b200 <version> sm_100a" */
 const char *qi_b200_version(void);

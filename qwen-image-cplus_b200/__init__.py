@@ -19,7 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libqipack_b200.so")
 SOURCES = ["qipack_b200.cu", "ptx.cuh", "quantize.cuh", "w4a16_gemm.cuh", "w4a16_gemv.cuh", "w4a4_gemm.cuh",
-           "shard.cuh"]
+           "w4a4_wide_gemm.cuh", "shard.cuh"]
 
 DTYPE_F32 = 0
 DTYPE_F16 = 1
@@ -51,11 +51,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
 class qi_packed_linear(ctypes.Structure):
     _fields_ = [("scheme", ctypes.c_uint32), ("group_size", ctypes.c_uint32), ("n", ctypes.c_int),
                 ("k", ctypes.c_int), ("weights", ctypes.c_void_p), ("scales", ctypes.c_void_p),
-                ("zeros", ctypes.c_void_p), ("bias", ctypes.c_void_p)]
+                ("zeros", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("weights_wide", ctypes.c_void_p)]
 
 
 class qi_linear_work(ctypes.Structure):
-    _fields_ = [("codes", ctypes.c_void_p), ("code_scales", ctypes.c_void_p), ("halves", ctypes.c_void_p)]
+    _fields_ = [("codes", ctypes.c_void_p), ("code_scales", ctypes.c_void_p), ("halves", ctypes.c_void_p),
+                ("wide", ctypes.c_void_p)]
 
 
 _P, _I, _LL, _ULL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_ulonglong
@@ -72,7 +73,19 @@ SIGNATURES = {
     "qi_w4a16_gemv_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
     "qi_w4a16_dequantize_ex": [_P, _P, _P, _P, _I, _I, _P],
     "qi_w4a4_group_dots_ex": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "qi_w4a4_widen_codes_ex": [_P, _P, _LL, _I, _P],
+    "qi_w4a4_quantize_activations_wide_ex": [_P, _I, _P, _P, _P, _I, _I, _P],
+    "qi_w4a4_gemm_wide_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
+    "qi_w4a4_group_dots_wide_ex": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "qi_linear": [ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _I, _LL, _I, _I, _P],
+    "qi_shard_plan": [_I, _I, _I, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+    "qi_shard_unique_id": [_P],
+    "qi_shard_create": [ctypes.POINTER(ctypes.c_void_p), _I, _I, _P],
+    "qi_shard_destroy": [_P],
+    "qi_shard_rank": [_P, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+    "qi_shard_all_gather": [_P, _P, _P, _I, _I, _I, _P],
+    "qi_shard_linear": [_P, ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _P, _I, _I,
+                        _I, _P],
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
     "qi_tune_w4a16_tile": [_I],
     "qi_tune_ablate": [_I],
@@ -162,6 +175,26 @@ def w4a4_group_dots_ex(a_codes, a_scales, w_codes, w_scales, y, dots, m: int, n:
                                        k, _p(stream))
 
 
+def w4a4_widen_codes_ex(codes, out_bytes, rows: int, k: int, stream=None) -> int:
+    return lib().qi_w4a4_widen_codes_ex(_p(codes), _p(out_bytes), rows, k, _p(stream))
+
+
+def w4a4_quantize_activations_wide_ex(x, x_dtype: int, codes, scales, out_bytes, m: int, k: int, stream=None) -> int:
+    return lib().qi_w4a4_quantize_activations_wide_ex(_p(x), x_dtype, _p(codes), _p(scales), _p(out_bytes), m, k,
+                                                      _p(stream))
+
+
+def w4a4_gemm_wide_ex(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,
+                      stream=None) -> int:
+    return lib().qi_w4a4_gemm_wide_ex(_p(a_bytes), _p(a_scales), _p(w_bytes), _p(w_scales), _p(bias), _p(y), y_dtype,
+                                      ldy, m, n, k, _p(stream))
+
+
+def w4a4_group_dots_wide_ex(a_bytes, a_scales, w_bytes, w_scales, y, dots, m: int, n: int, k: int, stream=None) -> int:
+    return lib().qi_w4a4_group_dots_wide_ex(_p(a_bytes), _p(a_scales), _p(w_bytes), _p(w_scales), _p(y), _p(dots), m,
+                                            n, k, _p(stream))
+
+
 def kernel_status() -> int:
     """Code of the first wait that gave up on the current device since the last call (0 = none)."""
     value = ctypes.c_uint(0)
@@ -184,18 +217,21 @@ def tune_ablate(flags: int) -> int:
 class PackedLinear:
     """One packed record resident on the device: scheme, n, k and the three regions."""
 
-    def __init__(self, scheme: int, n: int, k: int, weights, scales, zeros=None, bias=None, group_size: int = 64):
+    def __init__(self, scheme: int, n: int, k: int, weights, scales, zeros=None, bias=None, group_size: int = 64,
+                 weights_wide=None):
         self.scheme, self.n, self.k, self.group_size = scheme, n, k, group_size
         self.weights, self.scales, self.zeros, self.bias = weights, scales, zeros, bias  # keep tensors alive
-        self.record = qi_packed_linear(scheme, group_size, n, k, _p(weights), _p(scales), _p(zeros), _p(bias))
+        self.weights_wide = weights_wide
+        self.record = qi_packed_linear(scheme, group_size, n, k, _p(weights), _p(scales), _p(zeros), _p(bias),
+                                       _p(weights_wide))
 
 
 class LinearWork:
     """The activation arena of transformer.cplus:649-651 (codes, code_scales, halves)."""
 
-    def __init__(self, codes, code_scales, halves):
-        self.codes, self.code_scales, self.halves = codes, code_scales, halves
-        self.work = qi_linear_work(_p(codes), _p(code_scales), _p(halves))
+    def __init__(self, codes, code_scales, halves, wide=None):
+        self.codes, self.code_scales, self.halves, self.wide = codes, code_scales, halves, wide
+        self.work = qi_linear_work(_p(codes), _p(code_scales), _p(halves), _p(wide))
 
 
 def linear(model: PackedLinear, work: LinearWork, input, output, rows: int, reuse_input: bool = False, *,
@@ -205,3 +241,54 @@ def linear(model: PackedLinear, work: LinearWork, input, output, rows: int, reus
     return lib().qi_linear(ctypes.byref(model.record), ctypes.byref(work.work), _p(input), input_dtype, _p(output),
                            output_dtype, model.n if ld_output is None else ld_output, rows, int(reuse_input),
                            _p(stream))
+
+
+# ---- column sharding over the GPUs of one box ------------------------------------------------------
+
+SHARD_ID_BYTES = 128
+
+
+def shard_plan(n: int, ranks: int, rank: int):
+    """(first_row, row_count) of the weight rows `rank` owns; raises where no legal split exists."""
+    first, count = ctypes.c_int(0), ctypes.c_int(0)
+    status = lib().qi_shard_plan(n, ranks, rank, ctypes.byref(first), ctypes.byref(count))
+    if status != 0:
+        raise ValueError(f"n={n} cannot be split over {ranks} ranks in multiples of 128 rows (status {status})")
+    return first.value, count.value
+
+
+def shard_unique_id() -> bytes:
+    buffer = ctypes.create_string_buffer(SHARD_ID_BYTES)
+    status = lib().qi_shard_unique_id(buffer)
+    if status != 0:
+        raise RuntimeError(f"qi_shard_unique_id: status {status}")
+    return buffer.raw
+
+
+class ShardContext:
+    """One rank's handle on the NCCL communicator of a sharded linear stack."""
+
+    def __init__(self, rank: int, ranks: int, unique_id: bytes):
+        self.handle = ctypes.c_void_p(0)
+        buffer = ctypes.create_string_buffer(unique_id, SHARD_ID_BYTES)
+        status = lib().qi_shard_create(ctypes.byref(self.handle), rank, ranks, buffer)
+        if status != 0:
+            raise RuntimeError(f"qi_shard_create: status {status}")
+        self.rank, self.ranks = rank, ranks
+
+    def all_gather(self, y_local, y_slabs, output_dtype: int, rows: int, n_local: int, stream=None) -> int:
+        return lib().qi_shard_all_gather(self.handle, _p(y_local), _p(y_slabs), output_dtype, rows, n_local, _p(stream))
+
+    def linear(self, model: PackedLinear, work: LinearWork, input, y_local, y_slabs, rows: int,
+               reuse_input: bool = False, *, input_dtype: int = DTYPE_F32, output_dtype: int = DTYPE_F32,
+               stream=None) -> int:
+        return lib().qi_shard_linear(self.handle, ctypes.byref(model.record), ctypes.byref(work.work), _p(input),
+                                     input_dtype, _p(y_local), _p(y_slabs), output_dtype, rows, int(reuse_input),
+                                     _p(stream))
+
+    def destroy(self) -> int:
+        if self.handle:
+            status = lib().qi_shard_destroy(self.handle)
+            self.handle = ctypes.c_void_p(0)
+            return status
+        return 0

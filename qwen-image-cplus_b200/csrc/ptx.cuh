@@ -252,6 +252,55 @@ __device__ __forceinline__ void setmaxnreg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGISTERS));
 }
 
+// ---- packed fp32 pairs (one instruction, two IEEE-rounded results) ------------------------------
+
+__device__ __forceinline__ uint64_t pack_f32x2(float low, float high) {
+    uint64_t packed;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "f"(low), "f"(high));
+    return packed;
+}
+
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t low, uint32_t high) {
+    uint64_t packed;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "r"(low), "r"(high));
+    return packed;
+}
+
+__device__ __forceinline__ void unpack_f32x2(uint64_t packed, float &low, float &high) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(low), "=f"(high) : "l"(packed));
+}
+
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// ---- cp.async (4-byte, global -> shared, per thread) --------------------------------------------
+
+__device__ __forceinline__ void cp_async_4(void *smem, const void *global) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem)), "l"(global) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+
+template <int PENDING>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+
 // ---- small utilities -----------------------------------------------------------------------
 
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {

@@ -12,6 +12,7 @@
 #include "w4a16_gemm.cuh"
 #include "w4a16_gemv.cuh"
 #include "w4a4_gemm.cuh"
+#include "w4a4_wide_gemm.cuh"
 
 namespace qi {
 namespace {
@@ -132,6 +133,31 @@ int launch_w4a4(const void *a_codes, const void *a_scales, const void *w_codes, 
     return static_cast<int>(cudaGetLastError());
 }
 
+template <int STAGES>
+int launch_w4a4_wide(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                     const float *bias, void *y, int32_t *dots, const GemmShape &shape, cudaStream_t stream, int device) {
+    using T = w4a4_wide::Tile<STAGES>;
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_bytes, shape.k, shape.m, static_cast<uint64_t>(shape.k),
+                  w4a4_wide::STAGE_K, w4a4_wide::BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return INVALID;
+    if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_bytes, shape.k, shape.n, static_cast<uint64_t>(shape.k),
+                  w4a4_wide::STAGE_K, w4a4_wide::BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return INVALID;
+    auto kernel = dots != nullptr ? w4a4_wide::gemm_kernel<STAGES, true> : w4a4_wide::gemm_kernel<STAGES, false>;
+    static bool configured[MAX_DEVICES][2];
+    if (!configured[device][dots != nullptr]) {
+        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (error != cudaSuccess) return static_cast<int>(error);
+        configured[device][dots != nullptr] = true;
+    }
+    const int tiles = ((shape.m + w4a4_wide::BM - 1) / w4a4_wide::BM) * ((shape.n + w4a4_wide::BN - 1) / w4a4_wide::BN);
+    const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+    kernel<<<grid, w4a4_wide::THREADS, T::SMEM_BYTES, stream>>>(map_a, map_w, static_cast<const __half *>(a_scales),
+                                                                static_cast<const __half *>(w_scales), bias, y, dots, shape);
+    return static_cast<int>(cudaGetLastError());
+}
+
 bool output_ok(const void *y, int y_dtype, long long ldy, int n) {
     if (y == nullptr || !aligned16(y) || ldy < n) return false;
     if (y_dtype == QI_DTYPE_F32) return ldy % 4 == 0;
@@ -216,6 +242,20 @@ int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, co
     return launch_w4a4<128, 4>(a_codes, a_scales, w_codes, w_scales, bias, y, dots, shape, stream, device);
 }
 
+int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                   const float *bias, void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n, int k,
+                   cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 128 != 0) return INVALID;
+    if (!a_bytes || !a_scales || !w_bytes || !w_scales) return INVALID;
+    if (!aligned16(a_bytes) || !aligned16(w_bytes) || (reinterpret_cast<uintptr_t>(a_scales) & 3) ||
+        (reinterpret_cast<uintptr_t>(w_scales) & 3) || !output_ok(y, y_dtype, ldy, n))
+        return INVALID;
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
+    return launch_w4a4_wide<6>(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
+}
+
 }  // namespace
 }  // namespace qi
 
@@ -230,8 +270,45 @@ int qi_w4a4_quantize_activations_ex(const void *x, int x_dtype, void *codes, voi
     if (!x || !codes || !scales || !aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 7) ||
         (reinterpret_cast<uintptr_t>(scales) & 1))
         return INVALID;
-    return static_cast<int>(launch_quantize_activations(x, x_dtype == QI_DTYPE_F16, codes, scales, m, k,
+    return static_cast<int>(launch_quantize_activations(x, x_dtype == QI_DTYPE_F16, codes, scales, nullptr, m, k,
                                                         static_cast<cudaStream_t>(stream)));
+}
+
+int qi_w4a4_quantize_activations_wide_ex(const void *x, int x_dtype, void *codes, void *scales, void *bytes, int m,
+                                         int k, void *stream) {
+    if (m < 0 || k <= 0 || k % 256 != 0) return INVALID;
+    if (x_dtype != QI_DTYPE_F32 && x_dtype != QI_DTYPE_F16) return INVALID;
+    if (m == 0) return 0;
+    if (!x || !scales || !bytes || !aligned16(x) || !aligned16(bytes) || (reinterpret_cast<uintptr_t>(codes) & 7) ||
+        (reinterpret_cast<uintptr_t>(scales) & 1))
+        return INVALID;
+    return static_cast<int>(launch_quantize_activations(x, x_dtype == QI_DTYPE_F16, codes, scales, bytes, m, k,
+                                                        static_cast<cudaStream_t>(stream)));
+}
+
+int qi_w4a4_widen_codes_ex(const void *codes, void *bytes, long long rows, int k, void *stream) {
+    if (rows < 0 || k <= 0 || k % 32 != 0) return INVALID;
+    if (rows == 0) return 0;
+    if (!codes || !bytes || !aligned16(codes) || !aligned16(bytes)) return INVALID;
+    const long long chunks = rows * (k / 32);
+    const long long blocks = (chunks + 255) / 256;
+    if (blocks > 0x7fffffffLL) return INVALID;
+    w4a4_wide::widen_codes_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(codes), static_cast<uint8_t *>(bytes), chunks);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int qi_w4a4_gemm_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                         const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
+    return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a4_group_dots_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                               float *y, int32_t *dots, int m, int n, int k, void *stream) {
+    if (dots == nullptr) return INVALID;
+    return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, nullptr, y, QI_DTYPE_F32, n, dots, m, n, k,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int qi_w4a4_quantize_activations(const float *x, void *codes, void *scales, int m, int k) {
@@ -301,7 +378,18 @@ int qi_linear(const qi_packed_linear *record, const qi_linear_work *work, const 
     if (input_dtype != QI_DTYPE_F32 && input_dtype != QI_DTYPE_F16) return INVALID;
     const int n = record->n, k = record->k;
     if (record->scheme == QI_SCHEME_W4A4_H256) {  // transformer.cplus:702-708
-        if (!work->codes || !work->code_scales) return INVALID;
+        if (!work->code_scales) return INVALID;
+        if (record->weights_wide != nullptr && work->wide != nullptr) {
+            // one byte per code on both sides: no unpacking inside the GEMM
+            if (!reuse_input) {
+                const int status = qi_w4a4_quantize_activations_wide_ex(input, input_dtype, work->codes, work->code_scales,
+                                                                        work->wide, rows, k, stream);
+                if (status != 0) return status;
+            }
+            return qi_w4a4_gemm_wide_ex(work->wide, work->code_scales, record->weights_wide, record->scales, record->bias,
+                                        output, output_dtype, ld_output, rows, n, k, stream);
+        }
+        if (!work->codes) return INVALID;
         if (!reuse_input) {
             const int status = qi_w4a4_quantize_activations_ex(input, input_dtype, work->codes, work->code_scales, rows, k, stream);
             if (status != 0) return status;
@@ -358,3 +446,5 @@ int qi_tune_ablate(int flags) {
 const char *qi_b200_version(void) { return "qipack_b200 0.1 sm_100a"; }
 
 }  // extern "C"
+
+#include "shard.cuh"

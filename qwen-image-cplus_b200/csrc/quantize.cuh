@@ -20,6 +20,8 @@
 // rounding; a lane whose quotient lies within 2^-16 of a rounding tie redoes it with the
 // IEEE division the reference uses, so the codes are identical.
 #pragma once
+#include <cuda_fp8.h>
+
 #include "ptx.cuh"
 
 namespace qi {
@@ -74,10 +76,12 @@ __device__ __forceinline__ void two_passes(float (&v)[16]) {
     for (int o = 0; o < 4; ++o) butterfly(v[o], v[o + 4], v[o + 8], v[o + 12]);
 }
 
-template <typename T>
+// WIDE: also (or only, when codes is null) write every code as one FP8 E4M3 byte, [m, k], the
+// operand layout of w4a4_wide_gemm.cuh.
+template <typename T, bool WIDE>
 __global__ void __launch_bounds__(QUANT_THREADS)
 quantize_activations_kernel(const T *__restrict__ x, uint8_t *__restrict__ codes, __half *__restrict__ scales,
-                            long long chunks) {
+                            uint8_t *__restrict__ bytes, long long chunks) {
     __shared__ __align__(16) float transpose[(QUANT_THREADS / 32) * 2 * REGION];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int half_warp = lane >> 4, l = lane & 15;
@@ -126,6 +130,8 @@ quantize_activations_kernel(const T *__restrict__ x, uint8_t *__restrict__ codes
     const float reciprocal = 1.0f / scale16;
 
     uint32_t packed[2] = {0u, 0u};
+    uint32_t wide[4] = {0u, 0u, 0u, 0u};
+    float previous = 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const float rounded = fmaf(v[i], reciprocal, MAGIC);
@@ -139,9 +145,19 @@ quantize_activations_kernel(const T *__restrict__ x, uint8_t *__restrict__ codes
         }
         bits = min(max(bits, MAGIC_BITS - 7), MAGIC_BITS + 7);
         packed[i >> 3] |= static_cast<uint32_t>(bits & 0xF) << (4 * (i & 7));
+        if (WIDE) {
+            const float code = __int_as_float(bits) - MAGIC;  // exact
+            if (i & 1) {
+                const uint32_t pair = __nv_cvt_float2_to_fp8x2(make_float2(previous, code), __NV_SATFINITE, __NV_E4M3);
+                wide[i >> 2] |= pair << (8 * (i & 2));
+            }
+            previous = code;
+        }
     }
     if (active) {
-        *reinterpret_cast<uint2 *>(codes + chunk * 128 + l * 8) = make_uint2(packed[0], packed[1]);
+        if (!WIDE || codes != nullptr)
+            *reinterpret_cast<uint2 *>(codes + chunk * 128 + l * 8) = make_uint2(packed[0], packed[1]);
+        if (WIDE) *reinterpret_cast<uint4 *>(bytes + chunk * 256 + l * 16) = make_uint4(wide[0], wide[1], wide[2], wide[3]);
         if ((l & 3) == 0) scales[chunk * 4 + (l >> 2)] = scale_half;
     }
 }
@@ -169,19 +185,27 @@ __global__ void f32_to_f16_kernel(const float *__restrict__ source, __half *__re
 
 }  // namespace
 
-inline cudaError_t launch_quantize_activations(const void *x, int x_is_half, void *codes, void *scales, int m, int k,
-                                        cudaStream_t stream) {
+inline cudaError_t launch_quantize_activations(const void *x, int x_is_half, void *codes, void *scales, void *bytes,
+                                               int m, int k, cudaStream_t stream) {
     const long long chunks = static_cast<long long>(m) * (k / 256);
     if (chunks == 0) return cudaSuccess;
     const int chunks_per_block = QUANT_THREADS / 16;
     const long long blocks = (chunks + chunks_per_block - 1) / chunks_per_block;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-    if (x_is_half)
-        quantize_activations_kernel<__half><<<static_cast<unsigned>(blocks), QUANT_THREADS, 0, stream>>>(
-            static_cast<const __half *>(x), static_cast<uint8_t *>(codes), static_cast<__half *>(scales), chunks);
-    else
-        quantize_activations_kernel<float><<<static_cast<unsigned>(blocks), QUANT_THREADS, 0, stream>>>(
-            static_cast<const float *>(x), static_cast<uint8_t *>(codes), static_cast<__half *>(scales), chunks);
+    const unsigned grid = static_cast<unsigned>(blocks);
+    uint8_t *c = static_cast<uint8_t *>(codes), *b = static_cast<uint8_t *>(bytes);
+    __half *s = static_cast<__half *>(scales);
+    if (bytes != nullptr) {
+        if (x_is_half)
+            quantize_activations_kernel<__half, true><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __half *>(x), c, s, b, chunks);
+        else
+            quantize_activations_kernel<float, true><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float *>(x), c, s, b, chunks);
+    } else {
+        if (x_is_half)
+            quantize_activations_kernel<__half, false><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __half *>(x), c, s, b, chunks);
+        else
+            quantize_activations_kernel<float, false><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float *>(x), c, s, b, chunks);
+    }
     return cudaGetLastError();
 }
 

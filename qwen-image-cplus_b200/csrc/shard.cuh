@@ -1,0 +1,166 @@
+// Column (N) sharding of a packed linear over the GPUs of one box: rank r of R holds weight rows
+// [r*N/R, (r+1)*N/R) (codes, scales, minimums are row-major per output, so a shard is a contiguous
+// slice of each region), computes y[:, r*N/R:(r+1)*N/R] with the ordinary kernels, and the slices
+// are all-gathered over NVLink with NCCL. The reference is single-GPU (runtime.cu:6-19 uses device
+// 0 only); this is new work with no counterpart there.
+//
+// One process per GPU. NCCL is not linked: it is looked up at run time (dlopen), so that a process
+// that already carries an NCCL (a PyTorch process, for instance) shares that copy and a
+// single-GPU user of this library needs none at all.
+#pragma once
+#include <dlfcn.h>
+
+#include "../../include/qipack_b200.h"
+
+namespace qi {
+namespace shard {
+
+constexpr int NCCL_ERROR_BASE = 10000;  // returned as NCCL_ERROR_BASE + ncclResult_t
+constexpr int NCCL_MISSING = 10100;     // no libnccl could be loaded
+constexpr int NCCL_UINT8 = 1, NCCL_FLOAT16 = 6, NCCL_FLOAT32 = 7;  // ncclDataType_t values (nccl.h)
+
+struct UniqueId {
+    char internal[QI_SHARD_ID_BYTES];
+};
+
+struct Nccl {
+    void *handle = nullptr;
+    int (*GetUniqueId)(UniqueId *) = nullptr;
+    int (*CommInitRank)(void **, int, UniqueId, int) = nullptr;
+    int (*CommDestroy)(void *) = nullptr;
+    int (*CommAbort)(void *) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    bool ok() const { return handle && GetUniqueId && CommInitRank && CommDestroy && AllGather; }
+};
+
+inline Nccl &nccl() {
+    static Nccl api;
+    if (api.handle == nullptr) {
+        const char *override_path = getenv("QI_NCCL_LIBRARY");
+        const char *candidates[] = {override_path, "libnccl.so.2", "libnccl.so"};
+        for (const char *name : candidates) {
+            if (name == nullptr) continue;
+            api.handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle != nullptr) break;
+        }
+        if (api.handle != nullptr) {
+            api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
+            api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+            api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+            api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(api.handle, "ncclCommAbort"));
+            api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
+            api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
+        }
+    }
+    return api;
+}
+
+struct Context {
+    uint32_t magic;
+    int rank, ranks, device;
+    void *comm;
+};
+constexpr uint32_t CONTEXT_MAGIC = 0x51495348;  // "QISH"
+
+inline Context *checked(void *context) {
+    Context *c = static_cast<Context *>(context);
+    return (c != nullptr && c->magic == CONTEXT_MAGIC) ? c : nullptr;
+}
+
+// Rows of an [n, ...] weight that rank `rank` of `ranks` owns. Every shard must itself be a legal
+// GEMM (a multiple of 128 output rows), so n must divide into ranks * 128.
+inline int plan(int n, int ranks, int rank, int *first_row, int *row_count) {
+    if (n <= 0 || ranks <= 0 || rank < 0 || rank >= ranks) return static_cast<int>(cudaErrorInvalidValue);
+    if (n % ranks != 0 || (n / ranks) % 128 != 0) return static_cast<int>(cudaErrorInvalidValue);
+    if (first_row) *first_row = rank * (n / ranks);
+    if (row_count) *row_count = n / ranks;
+    return 0;
+}
+
+}  // namespace shard
+}  // namespace qi
+
+extern "C" {
+
+int qi_shard_plan(int n, int ranks, int rank, int *first_row, int *row_count) {
+    return qi::shard::plan(n, ranks, rank, first_row, row_count);
+}
+
+int qi_shard_unique_id(void *id) {
+    using namespace qi::shard;
+    if (id == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    Nccl &api = nccl();
+    if (!api.ok()) return NCCL_MISSING;
+    const int result = api.GetUniqueId(static_cast<UniqueId *>(id));
+    return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
+int qi_shard_create(void **context, int rank, int ranks, const void *id) {
+    using namespace qi::shard;
+    if (context == nullptr || id == nullptr || ranks < 1 || rank < 0 || rank >= ranks)
+        return static_cast<int>(cudaErrorInvalidValue);
+    *context = nullptr;
+    Nccl &api = nccl();
+    if (!api.ok()) return NCCL_MISSING;
+    int device = 0;
+    cudaError_t error = cudaGetDevice(&device);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    Context *c = new Context{CONTEXT_MAGIC, rank, ranks, device, nullptr};
+    UniqueId unique;
+    memcpy(&unique, id, sizeof(unique));
+    const int result = api.CommInitRank(&c->comm, ranks, unique, rank);
+    if (result != 0) {
+        delete c;
+        return NCCL_ERROR_BASE + result;
+    }
+    *context = c;
+    return 0;
+}
+
+int qi_shard_destroy(void *context) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    const int result = c->comm ? nccl().CommDestroy(c->comm) : 0;
+    c->magic = 0;
+    delete c;
+    return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
+int qi_shard_rank(void *context, int *rank, int *ranks) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    if (rank) *rank = c->rank;
+    if (ranks) *ranks = c->ranks;
+    return 0;
+}
+
+int qi_shard_all_gather(void *context, const void *y_local, void *y_slabs, int output_dtype, int rows, int n_local,
+                        void *stream) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr || y_local == nullptr || y_slabs == nullptr || rows <= 0 || n_local <= 0)
+        return static_cast<int>(cudaErrorInvalidValue);
+    if (output_dtype != QI_DTYPE_F32 && output_dtype != QI_DTYPE_F16) return static_cast<int>(cudaErrorInvalidValue);
+    const size_t count = static_cast<size_t>(rows) * n_local;
+    const int result = nccl().AllGather(y_local, y_slabs, count, output_dtype == QI_DTYPE_F16 ? NCCL_FLOAT16 : NCCL_FLOAT32,
+                                        c->comm, static_cast<cudaStream_t>(stream));
+    return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
+int qi_shard_linear(void *context, const qi_packed_linear *local_record, const qi_linear_work *work, const void *input,
+                    int input_dtype, void *y_local, void *y_slabs, int output_dtype, int rows, int reuse_input,
+                    void *stream) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr || local_record == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    if (local_record->n % 128 != 0) return static_cast<int>(cudaErrorInvalidValue);
+    const int status = qi_linear(local_record, work, input, input_dtype, y_local, output_dtype, local_record->n, rows,
+                                 reuse_input, stream);
+    if (status != 0 || y_slabs == nullptr || c->ranks == 1) return status;
+    return qi_shard_all_gather(context, y_local, y_slabs, output_dtype, rows, local_record->n, stream);
+}
+
+}  // extern "C"

@@ -34,6 +34,12 @@ constexpr int THREADS = 512;
 constexpr int STAGE_K = 128;  // int8 inputs per swizzle row = two 64-groups
 constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, WIDEN_WARP0 = 4, WIDEN_WARPS = 4, FOLD_WARP0 = 8, FOLD_WARPS = 8;
 
+// setmaxnreg can only hand out what the launch allocated: 65536 / 512 = 128 registers per thread.
+// Asking for more than that pool blocks the warpgroup for ever, so the split is checked here.
+constexpr int LAUNCH_REGISTERS = 128, CONTROL_REGISTERS = 56, WIDEN_REGISTERS = 80, FOLD_REGISTERS = 184;
+static_assert(128 * (CONTROL_REGISTERS + WIDEN_REGISTERS + 2 * FOLD_REGISTERS) <= THREADS * LAUNCH_REGISTERS,
+              "setmaxnreg.inc would wait for registers that do not exist");
+
 template <int BN, int STAGES>
 struct Tile {
     static constexpr int BM = 128;
@@ -111,7 +117,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // Warpgroup 0 = control, 1 = widen, 2-3 = fold. The fold warps hold the fp32 accumulators
     // of the whole tile, so registers move to them from the other two warpgroups.
     if (warp < WIDEN_WARP0) {
-      setmaxnreg_dec<56>();
+      setmaxnreg_dec<CONTROL_REGISTERS>();
       if (warp == PRODUCER_WARP) {
         if (lane == 0) {
             prefetch_tensormap(&map_a);
@@ -159,7 +165,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
       }
     } else if (warp < FOLD_WARP0) {
-        setmaxnreg_dec<80>();
+        setmaxnreg_dec<WIDEN_REGISTERS>();
         const int t = threadIdx.x - WIDEN_WARP0 * 32;  // 0..127
         uint32_t iteration = 0;
         bool alive = true;
@@ -217,7 +223,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
         }
     } else {
-        setmaxnreg_inc<184>();
+        setmaxnreg_inc<FOLD_REGISTERS>();
         constexpr int COLUMNS = BN / 2;  // per thread
         const int quadrant = warp & 3, column_half = (warp - FOLD_WARP0) >> 2;
         uint32_t iteration = 0, group_count = 0;

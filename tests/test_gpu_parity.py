@@ -356,3 +356,109 @@ def test_linear_dispatches_like_the_reference(qi):
             outputs.append(y)
     bad = qi.PackedLinear(3, n, k, xd, xd)
     assert qi.linear(bad, work, xd, outputs[0], rows) == qi.CUDA_ERROR_INVALID_VALUE
+
+
+# ---- W4A4 on byte-wide (E4M3) operands ---------------------------------------------------------------
+
+def e4m3_of_codes(codes):
+    """Expected output of qi_w4a4_widen_codes_ex: the FP8 E4M3 encoding of each code in -8..7."""
+    magnitude = np.array([0x00, 0x38, 0x40, 0x44, 0x48, 0x4A, 0x4C, 0x4E, 0x50], dtype=np.uint8)
+    values = qo.unpack_codes(codes, True).astype(np.int32)
+    return (magnitude[np.abs(values)] | np.where(values < 0, 0x80, 0)).astype(np.uint8)
+
+
+def test_widen_codes_matches_e4m3_table(qi):
+    rng = np.random.default_rng(91)
+    rows, k = 96, 640
+    codes = rng.integers(0, 256, size=(rows, k // 2), dtype=np.uint8)  # includes -8
+    out = torch.zeros(rows, k, dtype=torch.uint8, device="cuda")
+    assert qi.w4a4_widen_codes_ex(up(codes), out, rows, k) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), e4m3_of_codes(codes))
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+def test_quantize_wide_writes_the_same_codes_as_bytes(qi, dtype):
+    rng = np.random.default_rng(93)
+    m, k = 300, 1024
+    x16 = qt.make_activations(rng, m, k)
+    x = x16 if dtype == "f16" else x16.astype(np.float32)
+    codes = torch.zeros(m, k // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(m, k // 64, dtype=torch.float16, device="cuda")
+    wide = torch.zeros(m, k, dtype=torch.uint8, device="cuda")
+    x_dtype = qi.DTYPE_F16 if dtype == "f16" else qi.DTYPE_F32
+    assert qi.w4a4_quantize_activations_wide_ex(up(x), x_dtype, codes, scales, wide, m, k) == 0
+    torch.cuda.synchronize()
+    expected_codes, expected_scales = qo.quantize_activations(x)
+    assert np.array_equal(codes.cpu().numpy(), expected_codes)
+    assert np.array_equal(half_bits(scales), expected_scales)
+    assert np.array_equal(wide.cpu().numpy(), e4m3_of_codes(expected_codes))
+    wide2 = torch.zeros(m, k, dtype=torch.uint8, device="cuda")
+    assert qi.w4a4_quantize_activations_wide_ex(up(x), x_dtype, None, scales, wide2, m, k) == 0  # bytes only
+    torch.cuda.synchronize()
+    assert torch.equal(wide, wide2)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (128, 256, 3072), (200, 160, 1280)])
+def test_w4a4_wide_gemm_bits_and_exact_dots(qi, m, n, k):
+    rng = np.random.default_rng(5000 + m + n + k)
+    w_codes, w_scales = qt.random_w4a4_pack(rng, n, k, 1e-3, 6e-3)
+    a_codes, a_scales = qt.random_w4a4_pack(rng, m, k, 0.05, 0.6)
+    a_wide, w_wide = (torch.zeros(r, k, dtype=torch.uint8, device="cuda") for r in (m, n))
+    assert qi.w4a4_widen_codes_ex(up(a_codes), a_wide, m, k) == 0
+    assert qi.w4a4_widen_codes_ex(up(w_codes), w_wide, n, k) == 0
+    y = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    dots = torch.full((m, n, k // 64), 12345, dtype=torch.int32, device="cuda")
+    args = (a_wide, up(a_scales), w_wide, up(w_scales))
+    assert qi.w4a4_group_dots_wide_ex(*args, y, dots, m, n, k) == 0
+    check_status(qi)
+    assert np.array_equal(dots.cpu().numpy(), qo.w4a4_group_dots(a_codes, w_codes))
+    expected = qo.w4a4_gemm(a_codes, a_scales, w_codes, w_scales)
+    assert np.array_equal(y.cpu().numpy(), expected)
+    bias = qt.make_bias(rng, n)
+    y16 = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    assert qi.w4a4_gemm_wide_ex(*args, up(bias), y16, qi.DTYPE_F16, n, m, n, k) == 0
+    check_status(qi)
+    distance, _ = qt.fp16_store_error(y16.cpu().numpy(), qo.w4a4_gemm(a_codes, a_scales, w_codes, w_scales, bias=bias))
+    assert distance <= FP16_STORE_ULPS
+
+
+def test_w4a4_wide_gemm_extreme_dots(qi):
+    # all codes +-7: every group dot is +-3136, the largest the format allows; fp32 accumulation must stay exact
+    m, n, k = 128, 128, 512
+    a_codes = np.full((m, k // 2), 0x77, dtype=np.uint8)
+    a_codes[1::2] = 0x99
+    w_codes = np.full((n, k // 2), 0x77, dtype=np.uint8)
+    w_codes[2::3] = 0x99
+    w_codes[5::7] = 0x97
+    ones = np.full((m, k // 64), np.float16(1.0)).view(np.uint16)
+    a_wide, w_wide = (torch.zeros(r, k, dtype=torch.uint8, device="cuda") for r in (m, n))
+    assert qi.w4a4_widen_codes_ex(up(a_codes), a_wide, m, k) == 0
+    assert qi.w4a4_widen_codes_ex(up(w_codes), w_wide, n, k) == 0
+    y = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    dots = torch.zeros(m, n, k // 64, dtype=torch.int32, device="cuda")
+    assert qi.w4a4_group_dots_wide_ex(a_wide, up(ones), w_wide, up(ones[:n]), y, dots, m, n, k) == 0
+    check_status(qi)
+    expected = qo.w4a4_group_dots(a_codes, w_codes)
+    assert np.abs(expected).max() == 3136
+    assert np.array_equal(dots.cpu().numpy(), expected)
+
+
+def test_linear_takes_the_wide_path_when_given_wide_operands(qi):
+    rng = np.random.default_rng(95)
+    rows, n, k = 256, 384, 768
+    x32 = qt.make_activations(rng, rows, k).astype(np.float32)
+    codes, scales = qt.pack_w4a4(qt.make_weights(rng, n, k))
+    wide_w = torch.zeros(n, k, dtype=torch.uint8, device="cuda")
+    assert qi.w4a4_widen_codes_ex(up(codes), wide_w, n, k) == 0
+    work = qi.LinearWork(torch.zeros(rows * k // 2, dtype=torch.uint8, device="cuda"),
+                         torch.zeros(rows * k // 64, dtype=torch.float16, device="cuda"),
+                         torch.zeros(rows * k, dtype=torch.float16, device="cuda"),
+                         wide=torch.zeros(rows * k, dtype=torch.uint8, device="cuda"))
+    record = qi.PackedLinear(qi.SCHEME_W4A4_H256, n, k, up(codes), up(scales), weights_wide=wide_w)
+    y = torch.zeros(rows, n, dtype=torch.float32, device="cuda")
+    assert qi.linear(record, work, up(x32), y, rows) == 0
+    check_status(qi)
+    a_codes, a_scales = qo.quantize_activations(x32)
+    assert np.array_equal(y.cpu().numpy(), qo.w4a4_gemm(a_codes, a_scales, codes, scales))
+    assert work.wide.abs().sum().item() > 0  # the byte arena was really used

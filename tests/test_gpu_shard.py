@@ -1,0 +1,91 @@
+"""Column-sharded packed linears on 2 GPUs through the C ABI (NCCL all-gather over NVLink).
+Skipped on a box with fewer than two GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+from oracle import qipack_oracle as qo
+from tests import qi_testing as qt
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _worker(rank, ranks, port, result_path):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=ranks)  # host channel for the id only
+    qi = entry.load_package()
+    qi.lib()
+    holder = [qi.shard_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(holder, src=0)
+    context = qi.ShardContext(rank, ranks, holder[0])
+    device = torch.device("cuda", rank)
+
+    def up(array):
+        return torch.from_numpy(np.ascontiguousarray(array)).to(device)
+
+    rng = np.random.default_rng(99)
+    m, n, k = 256, 768, 1024
+    w16 = qt.make_weights(rng, n, k)
+    x32 = qt.make_activations(rng, m, k).astype(np.float32)
+    first, count = qi.shard_plan(n, ranks, rank)
+    work = qi.LinearWork(torch.zeros(m * k // 2, dtype=torch.uint8, device=device),
+                         torch.zeros(m * k // 64, dtype=torch.float16, device=device),
+                         torch.zeros(m * k, dtype=torch.float16, device=device),
+                         wide=torch.zeros(m * k, dtype=torch.uint8, device=device))
+    ok = True
+    # scheme 6, packed and byte-wide weights
+    codes, scales = qt.pack_w4a4(w16)
+    a_codes, a_scales = qo.quantize_activations(x32)
+    expected = qo.w4a4_gemm(a_codes, a_scales, codes, scales)
+    for wide in (False, True):
+        shard_codes = up(codes[first:first + count])
+        wide_w = None
+        if wide:
+            wide_w = torch.zeros(count, k, dtype=torch.uint8, device=device)
+            assert qi.w4a4_widen_codes_ex(shard_codes, wide_w, count, k) == 0
+        record = qi.PackedLinear(qi.SCHEME_W4A4_H256, count, k, shard_codes, up(scales[first:first + count]),
+                                 weights_wide=wide_w)
+        y_local = torch.zeros(m, count, dtype=torch.float32, device=device)
+        y_slabs = torch.zeros(ranks, m, count, dtype=torch.float32, device=device)
+        assert context.linear(record, work, up(x32), y_local, y_slabs, m) == 0
+        torch.cuda.synchronize()
+        assert qi.kernel_status() == 0
+        rebuilt = y_slabs.cpu().numpy().transpose(1, 0, 2).reshape(m, n)
+        ok = ok and np.array_equal(rebuilt, expected)
+    # scheme 5, fp16 output
+    codes5, scales5, minimums5 = qt.pack_w4a16(w16)
+    record5 = qi.PackedLinear(qi.SCHEME_W4A16, count, k, up(codes5[first:first + count]),
+                              up(scales5[first:first + count]), up(minimums5[first:first + count]))
+    y_local = torch.zeros(m, count, dtype=torch.float16, device=device)
+    y_slabs = torch.zeros(ranks, m, count, dtype=torch.float16, device=device)
+    assert context.linear(record5, work, up(x32), y_local, y_slabs, m, output_dtype=qi.DTYPE_F16) == 0
+    torch.cuda.synchronize()
+    expected5 = qo.w4a16_gemm(qo.f32_to_f16(x32).view(np.float16), codes5, scales5, minimums5)
+    rebuilt5 = y_slabs.cpu().numpy().transpose(1, 0, 2).reshape(m, n).astype(np.float32)
+    ok = ok and qt.max_relative_error(rebuilt5, expected5) <= 1e-3
+    assert context.destroy() == 0
+    dist.barrier()
+    if rank == 0:
+        with open(result_path, "w") as handle:
+            handle.write("ok" if ok else "mismatch")
+    dist.destroy_process_group()
+
+
+def test_two_ranks_all_gather_the_unsharded_result(tmp_path):
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    result = tmp_path / "result.txt"
+    mp.spawn(_worker, args=(2, port, str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"

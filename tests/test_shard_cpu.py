@@ -1,0 +1,97 @@
+"""Host-side logic of the column sharding, on CPU: the row plan, and two gloo ranks that each
+compute their shard with the oracle, all-gather the slabs [ranks][rows][n_local] and rebuild the
+row-major result the unsharded operator gives."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+from oracle import qipack_oracle as qo
+from tests import qi_testing as qt
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def qi():
+    module = entry.load_package()
+    if not os.path.exists(module.LIB_PATH):
+        module.build()
+    return module
+
+
+def test_shard_plan_covers_every_row_once(qi):
+    for n in (3072, 9216, 12288, 18432):
+        for ranks in (1, 2, 4, 8):
+            rows = []
+            for rank in range(ranks):
+                first, count = qi.shard_plan(n, ranks, rank)
+                assert count % 128 == 0 and first == rank * count
+                rows.extend(range(first, first + count))
+            assert rows == list(range(n))
+
+
+def test_shard_plan_rejects_illegal_splits(qi):
+    with pytest.raises(ValueError):
+        qi.shard_plan(3072, 5, 0)       # does not divide
+    with pytest.raises(ValueError):
+        qi.shard_plan(512, 8, 0)        # 64 rows per rank: not a legal GEMM
+    with pytest.raises(ValueError):
+        qi.shard_plan(3072, 2, 2)       # rank out of range
+    with pytest.raises(ValueError):
+        qi.shard_plan(0, 1, 0)
+
+
+def slabs_to_row_major(slabs: np.ndarray) -> np.ndarray:
+    """[ranks, rows, n_local] -> [rows, ranks * n_local]: column block r is rank r's slice."""
+    ranks, rows, n_local = slabs.shape
+    return np.ascontiguousarray(slabs.transpose(1, 0, 2).reshape(rows, ranks * n_local))
+
+
+def _worker(rank, ranks, port, result_path):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=ranks)
+    qi = entry.load_package()
+    rng = np.random.default_rng(2024)  # same data on every rank
+    m, n, k = 32, 512, 512
+    w16 = qt.make_weights(rng, n, k)
+    x16 = qt.make_activations(rng, m, k)
+    first, count = qi.shard_plan(n, ranks, rank)
+    outputs = {}
+    # W4A4: the packer works row by row, so packing a row slice equals slicing the packed matrix
+    codes, scales = qt.pack_w4a4(w16)
+    shard_codes, shard_scales = qt.pack_w4a4(w16[first:first + count])
+    assert np.array_equal(shard_codes, codes[first:first + count])
+    assert np.array_equal(shard_scales, scales[first:first + count])
+    a_codes, a_scales = qo.quantize_activations(x16)
+    local = qo.w4a4_gemm(a_codes, a_scales, shard_codes, shard_scales)
+    gathered = [torch.empty(m, count) for _ in range(ranks)]
+    dist.all_gather(gathered, torch.from_numpy(local))
+    outputs["w4a4"] = (slabs_to_row_major(torch.stack(gathered).numpy()),
+                       qo.w4a4_gemm(a_codes, a_scales, codes, scales))
+    codes5, scales5, minimums5 = qt.pack_w4a16(w16)
+    local5 = qo.w4a16_gemm(x16, codes5[first:first + count], scales5[first:first + count],
+                           minimums5[first:first + count])
+    gathered5 = [torch.empty(m, count) for _ in range(ranks)]
+    dist.all_gather(gathered5, torch.from_numpy(local5))
+    outputs["w4a16"] = (slabs_to_row_major(torch.stack(gathered5).numpy()),
+                        qo.w4a16_gemm(x16, codes5, scales5, minimums5))
+    ok = all(np.array_equal(a, b) for a, b in outputs.values())
+    dist.barrier()
+    if rank == 0:
+        with open(result_path, "w") as handle:
+            handle.write("ok" if ok else "mismatch")
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_rebuild_the_unsharded_result(tmp_path):
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    result = tmp_path / "result.txt"
+    mp.spawn(_worker, args=(2, port, str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"
