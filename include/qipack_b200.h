@@ -196,6 +196,7 @@ int qi_kernel_status(unsigned int *status);
  * parts of the GEMM kernels off to see what bounds them (results are then wrong). */
 int qi_tune_w4a16_tile(int tile);
 int qi_tune_ablate(int flags);
+int qi_tune_w4a4_wide_single(int single); /* 1: byte-operand W4A4 on single CTAs instead of CTA pairs */
 
 /* "qipack_b200 <version> sm_100a" */
 const char *qi_b200_version(void);

@@ -19,7 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libqipack_b200.so")
 SOURCES = ["qipack_b200.cu", "ptx.cuh", "quantize.cuh", "w4a16_gemm.cuh", "w4a16_gemv.cuh", "w4a4_gemm.cuh",
-           "w4a4_wide_gemm.cuh", "shard.cuh"]
+           "w4a4_wide_gemm.cuh", "w4a4_pair_gemm.cuh", "shard.cuh"]
 
 DTYPE_F32 = 0
 DTYPE_F16 = 1
@@ -89,6 +89,7 @@ SIGNATURES = {
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
     "qi_tune_w4a16_tile": [_I],
     "qi_tune_ablate": [_I],
+    "qi_tune_w4a4_wide_single": [_I],
 }
 
 _lib = None
@@ -206,6 +207,10 @@ def kernel_status() -> int:
 
 def tune_w4a16_tile(tile: int) -> int:
     return lib().qi_tune_w4a16_tile(tile)
+
+
+def tune_w4a4_wide_single(single: int) -> int:
+    return lib().qi_tune_w4a4_wide_single(single)
 
 
 def tune_ablate(flags: int) -> int:

@@ -100,6 +100,15 @@ __device__ __forceinline__ bool mbarrier_wait(uint64_t *barrier, uint32_t parity
     return false;
 }
 
+// The same for a whole converged warp: lane 0 polls, the others wait for it at a warp barrier
+// (32 lanes polling one barrier word only multiply the shared-memory traffic).
+__device__ __forceinline__ bool mbarrier_wait_warp(uint64_t *barrier, uint32_t parity, uint32_t *status,
+                                                   uint32_t code, int lane) {
+    uint32_t ok = 1;
+    if (lane == 0) ok = mbarrier_wait(barrier, parity, status, code) ? 1u : 0u;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---- TMA ---------------------------------------------------------------------------------
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
@@ -299,6 +308,114 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+
+// ---- thread-block clusters and cta_group::2 (one MMA over a pair of CTAs) ------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+// All threads of both CTAs; orders shared-memory and barrier initialisation before remote use.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_address, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ void mbarrier_arrive_cluster(uint32_t cluster_address) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+
+// Shared-memory addresses of the even CTA of a pair: bit 24 of a shared::cluster address is the
+// rank within the pair.
+constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;
+
+// TMA load whose completion bytes are counted on the pair leader's mbarrier (no multicast: each CTA
+// fetches its own tile into its own shared memory).
+__device__ __forceinline__ void tma_load_2d_pair(void *smem, const CUtensorMap *map, uint64_t *barrier, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(barrier) & PAIR_LEADER_MASK), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *slot, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+// Arrives on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t *barrier) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(barrier)),
+                 "h"(both)
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 16 TMEM lanes x 32 columns in the fragment layout of an m16n8 accumulator, repeated 4 times along
+// the columns: with i = thread index, register 4x+0, 4x+1 = lane i/4, columns 8x + 2(i%4) + {0,1};
+// register 4x+2, 4x+3 = lane i/4 + 8, same columns. `address` carries the first of the 16 lanes.
+__device__ __forceinline__ void tmem_load_16x256_x4(uint32_t address, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address)
+        : "memory");
+}
+
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_load_32x16(uint32_t address, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address)
+        : "memory");
 }
 
 // ---- small utilities -----------------------------------------------------------------------

@@ -13,6 +13,7 @@
 #include "w4a16_gemv.cuh"
 #include "w4a4_gemm.cuh"
 #include "w4a4_wide_gemm.cuh"
+#include "w4a4_pair_gemm.cuh"
 
 namespace qi {
 namespace {
@@ -158,6 +159,34 @@ int launch_w4a4_wide(const void *a_bytes, const void *a_scales, const void *w_by
     return static_cast<int>(cudaGetLastError());
 }
 
+// 0 = 256x256 tiles on CTA pairs; 1 = 128x128 tiles on single CTAs (w4a4_wide_gemm.cuh). Tuning hook.
+int g_w4a4_wide_single = 0;
+
+int launch_w4a4_pair(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                     const float *bias, void *y, int32_t *dots, const GemmShape &shape, cudaStream_t stream, int device) {
+    namespace wp = w4a4_pair;
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_bytes, shape.k, shape.m, static_cast<uint64_t>(shape.k),
+                  wp::STAGE_K, wp::BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return INVALID;
+    if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_bytes, shape.k, shape.n, static_cast<uint64_t>(shape.k),
+                  wp::STAGE_K, wp::BN / 2, CU_TENSOR_MAP_SWIZZLE_128B))
+        return INVALID;
+    auto kernel = dots != nullptr ? wp::gemm_kernel<true> : wp::gemm_kernel<false>;
+    static bool configured[MAX_DEVICES][2];
+    if (!configured[device][dots != nullptr]) {
+        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wp::SMEM_BYTES);
+        if (error != cudaSuccess) return static_cast<int>(error);
+        configured[device][dots != nullptr] = true;
+    }
+    const int tiles = ((shape.m + 2 * wp::BM - 1) / (2 * wp::BM)) * ((shape.n + wp::BN - 1) / wp::BN);
+    const int pairs = sm_count(device) / 2;
+    const int grid = 2 * (tiles < pairs ? tiles : pairs);  // the kernel carries __cluster_dims__(2, 1, 1)
+    kernel<<<grid, wp::THREADS, wp::SMEM_BYTES, stream>>>(map_a, map_w, static_cast<const __half *>(a_scales),
+                                                          static_cast<const __half *>(w_scales), bias, y, dots, shape);
+    return static_cast<int>(cudaGetLastError());
+}
+
 bool output_ok(const void *y, int y_dtype, long long ldy, int n) {
     if (y == nullptr || !aligned16(y) || ldy < n) return false;
     if (y_dtype == QI_DTYPE_F32) return ldy % 4 == 0;
@@ -253,7 +282,9 @@ int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_byte
     const int device = current_device();
     if (device < 0) return INVALID;
     const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
-    return launch_w4a4_wide<6>(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
+    if (g_w4a4_wide_single)
+        return launch_w4a4_wide<6>(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
+    return launch_w4a4_pair(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
 }
 
 }  // namespace
@@ -440,6 +471,11 @@ int qi_tune_w4a16_tile(int tile) {
 // Tuning only: switches parts of the GEMM kernels off to see what bounds them (results are then wrong).
 int qi_tune_ablate(int flags) {
     g_ablate = flags;
+    return 0;
+}
+
+int qi_tune_w4a4_wide_single(int single) {
+    g_w4a4_wide_single = single != 0;
     return 0;
 }
 

@@ -26,6 +26,7 @@ namespace qi {
 
 __device__ uint32_t g_status = 0;  // first failed wait of any kernel of this library (0 = none)
 
+
 struct GemmShape {
     int m, n, k;
     long long ldy;    // elements between rows of y

@@ -209,7 +209,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             float2 values[BN / 64];
 #pragma unroll
             for (int p = 0; p < BN / 64; ++p) values[p] = __half22float2(sw_ring[(it % SCALE_RING) * BN + p * 64 + t]);
-            if (!mbarrier_wait(&empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x4000 | s)) break;
+            if (!mbarrier_wait_warp(&empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x4000 | s, lane)) break;
             float *sw_stage = sw_tile + s * 2 * BN;
 #pragma unroll
             for (int p = 0; p < BN / 64; ++p) {
@@ -240,14 +240,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 const uint32_t phase = (iteration / STAGES) & 1;
                 const float2 sa_pair = __half22float2(sa_next);
                 if (ks + 1 < k_stages) sa_next = __ldg(reinterpret_cast<const __half2 *>(sa_row + 2 * ks + 2));
-                if (!mbarrier_wait(&scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x3000 | s)) { alive = false; break; }
+                if (!mbarrier_wait_warp(&scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x3000 | s, lane)) { alive = false; break; }
                 const float *sw_stage = sw_tile + s * 2 * BN + slice * COLUMNS;
 #pragma unroll
                 for (int gl = 0; gl < 2; ++gl, ++group_count) {
                     const uint32_t buffer = group_count % BUFFERS, buffer_phase = (group_count / BUFFERS) & 1;
                     const float sa = gl == 0 ? sa_pair.x : sa_pair.y;
                     const uint64_t sa2 = pack_f32x2(sa, sa);
-                    if (!mbarrier_wait(&dot_full[buffer], buffer_phase, &g_status, STATUS_WAIT_TMEM_FULL | 0x3000 | buffer)) { alive = false; break; }
+                    if (!mbarrier_wait_warp(&dot_full[buffer], buffer_phase, &g_status, STATUS_WAIT_TMEM_FULL | 0x3000 | buffer, lane)) { alive = false; break; }
                     tcgen05_fence_after();
                     uint32_t r[32];
                     if (!(shape.ablate & 8)) {

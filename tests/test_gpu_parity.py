@@ -399,8 +399,17 @@ def test_quantize_wide_writes_the_same_codes_as_bytes(qi, dtype):
     assert torch.equal(wide, wide2)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (128, 256, 3072), (200, 160, 1280)])
-def test_w4a4_wide_gemm_bits_and_exact_dots(qi, m, n, k):
+@pytest.fixture(params=["pair", "single"])
+def wide_kernel(request, qi):
+    """Both byte-operand kernels: 256x256 tiles on CTA pairs (default) and 128x128 on single CTAs."""
+    qi.tune_w4a4_wide_single(1 if request.param == "single" else 0)
+    yield request.param
+    qi.tune_w4a4_wide_single(0)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (128, 256, 3072), (200, 160, 1280),
+                                   (640, 768, 256)])
+def test_w4a4_wide_gemm_bits_and_exact_dots(qi, wide_kernel, m, n, k):
     rng = np.random.default_rng(5000 + m + n + k)
     w_codes, w_scales = qt.random_w4a4_pack(rng, n, k, 1e-3, 6e-3)
     a_codes, a_scales = qt.random_w4a4_pack(rng, m, k, 0.05, 0.6)
@@ -423,7 +432,7 @@ def test_w4a4_wide_gemm_bits_and_exact_dots(qi, m, n, k):
     assert distance <= FP16_STORE_ULPS
 
 
-def test_w4a4_wide_gemm_extreme_dots(qi):
+def test_w4a4_wide_gemm_extreme_dots(qi, wide_kernel):
     # all codes +-7: every group dot is +-3136, the largest the format allows; fp32 accumulation must stay exact
     m, n, k = 128, 128, 512
     a_codes = np.full((m, k // 2), 0x77, dtype=np.uint8)
