@@ -11,6 +11,7 @@
 #include "quantize.cuh"
 #include "w4a16_gemm.cuh"
 #include "w4a16_gemv.cuh"
+#include "w4a16_pair_gemm.cuh"
 #include "w4a4_gemm.cuh"
 #include "w4a4_wide_gemm.cuh"
 #include "w4a4_pair_gemm.cuh"
@@ -80,7 +81,8 @@ bool make_map(CUtensorMap *map, CUtensorMapDataType type, int element_bytes, con
 
 // ---- tile selection -----------------------------------------------------------------------------
 
-// 0 = choose by shape; otherwise forces one W4A16 tile: 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256.
+// 0 = choose by shape; otherwise forces one W4A16 tile: 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256,
+// 5 = 256x256 on a pair of CTAs.
 int g_w4a16_tile = 0;
 int g_ablate = 0;  // tuning only, see GemmShape::ablate
 
@@ -106,6 +108,33 @@ int launch_w4a16(const void *x_half, const void *codes, const void *scales, cons
     const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
     kernel<<<grid, w4a16::THREADS, T::SMEM_BYTES, stream>>>(map_x, map_codes, static_cast<const __half *>(scales),
                                                             static_cast<const __half *>(minimums), bias, y, shape);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <int STAGES>
+int launch_w4a16_pair(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
+                      void *y, const GemmShape &shape, cudaStream_t stream, int device) {
+    namespace wp = w4a16_pair;
+    using T = wp::Tile<STAGES>;
+    CUtensorMap map_x, map_codes;
+    if (!make_map(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x_half, shape.k, shape.m,
+                  static_cast<uint64_t>(shape.k) * 2, 64, wp::BM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return INVALID;
+    if (!make_map(&map_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, shape.k / 2, shape.n,
+                  static_cast<uint64_t>(shape.k) / 2, 32, wp::BN / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return INVALID;
+    auto kernel = wp::gemm_kernel<STAGES>;
+    static bool configured[MAX_DEVICES];
+    if (!configured[device]) {
+        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (error != cudaSuccess) return static_cast<int>(error);
+        configured[device] = true;
+    }
+    const int tiles = ((shape.m + 2 * wp::BM - 1) / (2 * wp::BM)) * ((shape.n + wp::BN - 1) / wp::BN);
+    const int pairs = sm_count(device) / 2;
+    const int grid = 2 * (tiles < pairs ? tiles : pairs);  // the kernel carries __cluster_dims__(2, 1, 1)
+    kernel<<<grid, wp::THREADS, T::SMEM_BYTES, stream>>>(map_x, map_codes, static_cast<const __half *>(scales),
+                                                         static_cast<const __half *>(minimums), bias, y, shape);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -241,12 +270,14 @@ int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const 
     const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
     int tile = g_w4a16_tile;
     if (tile == 0) {
-        // tall tiles halve the unpacking work per MMA; take them when they still fill the machine
+        // Measured on B200 (4096 x {3072, 9216, 12288} x {3072, 12288}, 1024 and 256 rows):
+        // 256x256 on one CTA wins when there are at least two full waves of such tiles; the same
+        // tile on a CTA pair (half the unpacking per CTA, overlapped epilogue, 74 tiles per wave)
+        // wins below that; 128x128 wins when even pairs would leave most of the machine idle.
         const int sms = sm_count(device);
         const long long tiles_256 = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
-        const long long tiles_256x128 = static_cast<long long>((m + 255) / 256) * ((n + 127) / 128);
-        if (m > 128 && tiles_256 >= 2LL * sms) tile = 4;
-        else if (m > 128 && tiles_256x128 >= sms) tile = 2;
+        if (tiles_256 >= 2LL * sms) tile = 4;
+        else if (tiles_256 * 4 >= sms) tile = 5;
         else tile = 1;
     }
     switch (tile) {
@@ -254,6 +285,7 @@ int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const 
         case 2: return launch_w4a16<2, 128, 4>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
         case 3: return launch_w4a16<1, 256, 4>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
         case 4: return launch_w4a16<2, 256, 3>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
+        case 5: return launch_w4a16_pair<6>(x_half, codes, scales, minimums, bias, y, shape, stream, device);
         default: return INVALID;
     }
 }
@@ -463,7 +495,7 @@ int qi_kernel_status(unsigned int *status) {
 
 // Forces one W4A16 tile (1..4) or returns to the shape heuristic (0). For tuning runs.
 int qi_tune_w4a16_tile(int tile) {
-    if (tile < 0 || tile > 4) return INVALID;
+    if (tile < 0 || tile > 5) return INVALID;
     g_w4a16_tile = tile;
     return 0;
 }

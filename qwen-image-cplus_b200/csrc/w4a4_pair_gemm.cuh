@@ -13,8 +13,8 @@
 //   warp 1      leader only: per group two tcgen05.mma.cta_group::2 kind::f8f6f4 (K = 32) into one of
 //               two TMEM buffers of 256 fp32 columns; commits arrive on both CTAs' barriers
 //   warps 2-3   stage sw of the stage's two groups (256 columns) as fp32
-//   warps 4-11  fold this CTA's 128 rows: thread = one row x 128 columns, tcgen05.ld 64 columns at a
-//               time; after the last load the warp releases the buffer on the LEADER's barrier
+//   warps 4-11  fold this CTA's 128 rows x 256 columns, 32 rows x 128 columns per warp; after its last
+//               load of a group the warp releases the TMEM buffer on the LEADER's barrier
 #pragma once
 #include "ptx.cuh"
 #include "w4a16_gemm.cuh"
@@ -29,10 +29,11 @@ constexpr int STAGE_K = 128;
 constexpr int BUFFERS = 2;     // TMEM buffers of BN fp32 columns
 constexpr int STAGES = 6;
 constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, SCALE_WARP0 = 2, SCALE_WARPS = 2, FOLD_WARP0 = 4, FOLD_WARPS = 8;
-constexpr int COLUMNS = BN / (FOLD_WARPS / 4);  // 128 per fold thread
+constexpr int COLUMNS = BN / (FOLD_WARPS / 4);  // columns per fold warp: 128
+constexpr bool DOUBLE_BUFFER = true;            // a second register set for the dots in flight
 // setmaxnreg can only hand out what the launch allocated: floor8(65536 / 384) = 168 registers per thread.
-// Two fold warps per scheduler, each with its whole 128-column accumulator row and 64 fetched dots in
-// registers: while one waits for its TMEM load the other has 128 independent packed operations to issue.
+// Two fold warps per scheduler, each with 128 accumulators and two sets of 32 fetched dots. Measured
+// against four warps per scheduler with 64 accumulators and one set (112 registers, spills): 1.7x faster.
 constexpr int LAUNCH_REGISTERS = 168, CONTROL_REGISTERS = 40, FOLD_REGISTERS = 232;
 static_assert(128 * CONTROL_REGISTERS + FOLD_WARPS * 32 * FOLD_REGISTERS <= THREADS * LAUNCH_REGISTERS,
               "setmaxnreg.inc would wait for registers that do not exist");
@@ -107,8 +108,8 @@ __device__ __forceinline__ void scale_role(const View &v, const __half *__restri
 // shared-memory broadcast per column and warp - more load wavefronts than the fp32 pipe has
 // cycles. In the fragment layout a thread's columns never change, so a group costs 16 eight-byte
 // loads of sw and 4 values of sa per thread.
-// Two alternating register sets: while the multiply / fused multiply-add of one 32-column
-// batch issue, the tcgen05.ld of the next batch is in flight.
+// With DOUBLE_BUFFER two register sets alternate (the tcgen05.ld of the next 32-column batch is in flight
+// during the arithmetic of this one).
 template <bool DUMP_DOTS>
 __device__ __forceinline__ void fold_role(const View &v, const __half *__restrict__ a_scales,
                                           const float *__restrict__ bias, void *__restrict__ y,
@@ -120,7 +121,7 @@ __device__ __forceinline__ void fold_role(const View &v, const __half *__restric
     const uint32_t tmem_lane = v.tmem_base + slice * COLUMNS + (static_cast<uint32_t>(quadrant * 32) << 16);
     const int my_tiles = v.pair < v.tiles ? (v.tiles - 1 - v.pair) / v.pairs + 1 : 0;
     const uint32_t total_groups = static_cast<uint32_t>(my_tiles) * v.groups;
-    uint32_t set[2][32];  // [16 * half + 4 * x + 2 * a + e]: rows fragment_row + 16 half + 8 a, columns 8 x + pair_column + e
+    uint32_t set[DOUBLE_BUFFER ? 2 : 1][32];  // [16 * half + 4 * x + 2 * a + e]: rows fragment_row + 16 half + 8 a, columns 8 x + pair_column + e
     bool alive = true;
 
     // Starts the load of batch `batch` of group `group_count`; the first batch of a group waits for its dots.
@@ -182,8 +183,8 @@ __device__ __forceinline__ void fold_role(const View &v, const __half *__restric
                 const float *sw_group = sw_stage + gl * BN;
 #pragma unroll
                 for (int b = 0; b < BATCHES; ++b) {
-                    uint32_t(&current)[32] = set[b & 1];
-                    uint32_t(&following)[32] = set[(b + 1) & 1];
+                    uint32_t(&current)[32] = set[DOUBLE_BUFFER ? (b & 1) : 0];
+                    uint32_t(&following)[32] = set[DOUBLE_BUFFER ? ((b + 1) & 1) : 0];
                     tmem_load_wait();  // `current` has landed; nothing else is in flight
                     const bool last_batch = b == BATCHES - 1;
                     const uint32_t next_group = group_count + (last_batch ? 1 : 0);
@@ -194,8 +195,8 @@ __device__ __forceinline__ void fold_role(const View &v, const __half *__restric
                         tcgen05_fence_before();
                         __syncwarp();
                         if (lane == 0) mbarrier_arrive_cluster(leader_dot_empty + buffer * 8);
-                        if (has_next) issued = issue(next_group, 0, following, false);  // only if its dots are already there
-                    } else {
+                        if (DOUBLE_BUFFER && has_next) issued = issue(next_group, 0, following, false);  // only if its dots are already there
+                    } else if (DOUBLE_BUFFER) {
                         issued = issue(group_count, b + 1, following, true);
                     }
                     if (DUMP_DOTS) {
@@ -229,7 +230,11 @@ __device__ __forceinline__ void fold_role(const View &v, const __half *__restric
                             }
                         }
                     }
-                    if (last_batch && has_next && !issued && alive) issue(next_group, 0, following, true);
+                    if (last_batch) {
+                        if (has_next && !issued && alive) issue(next_group, 0, following, true);
+                    } else if (!DOUBLE_BUFFER) {
+                        issue(group_count, b + 1, following, true);
+                    }
                 }
                 if (!alive) break;
             }

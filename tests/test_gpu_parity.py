@@ -152,7 +152,7 @@ def test_w4a16_dequantize_bit_exact(qi):
         assert np.array_equal(half_bits(out), expected.view(np.uint16)), source
 
 
-@pytest.mark.parametrize("tile", [1, 2, 3, 4])
+@pytest.mark.parametrize("tile", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 256, 512), (384, 640, 1024), (128, 384, 3072)])
 def test_w4a16_gemm_matches_oracle(qi, tile, m, n, k):
     rng = np.random.default_rng(2000 + m + n + k)
