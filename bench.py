@@ -200,14 +200,22 @@ def run_b200(args):
     def step(record_gemm_events=None):
         for layer in layers:
             k, n_local = layer["k"], layer["n_local"]
-            status = qi.w4a4_quantize_activations_wide_ex(layer["x"], qi.DTYPE_F16, None, layer["a_scales"],
-                                                          layer["a_wide"], m, k, stream_handle)
+            if args.w4a4_path == "wide":
+                status = qi.w4a4_quantize_activations_wide_ex(layer["x"], qi.DTYPE_F16, None, layer["a_scales"],
+                                                              layer["a_wide"], m, k, stream_handle)
+            else:
+                status = qi.w4a4_quantize_activations_ex(layer["x"], qi.DTYPE_F16, layer["a_codes"], layer["a_scales"],
+                                                         m, k, stream_handle)
             assert status == 0, f"quantise {layer['name']}: cuda status {status}"
             if record_gemm_events is not None:
                 start = torch.cuda.Event(enable_timing=True)
                 start.record(stream)
-            status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"], None,
-                                          layer["y_local"], qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
+            if args.w4a4_path == "wide":
+                status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
+                                              None, layer["y_local"], qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
+            else:
+                status = qi.w4a4_gemm_ex(layer["a_codes"], layer["a_scales"], layer["w_codes"], layer["w_scales"], None,
+                                         layer["y_local"], qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
             assert status == 0, f"gemm {layer['name']}: cuda status {status}"
             if record_gemm_events is not None:
                 stop = torch.cuda.Event(enable_timing=True)
@@ -291,16 +299,17 @@ def run_b200(args):
         result = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "int4 codes (one E4M3 byte each), exact fp32 tensor-core group dots, fp32 fold",
+            "scaling": "strong", "vs_baseline": None, "dtype": ("int4 codes, exact int8 tensor-core group dots, fp32 fold" if args.w4a4_path == "packed" else
+                      "int4 codes (one E4M3 byte each), exact fp32 tensor-core group dots, fp32 fold"),
             "data": "synthetic: W ~ N(0,0.02) rotated (H256) and quantised to int4 g64 on the device, "
                     "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
-            "config": {"workload": WORKLOAD, "m": m, "ops_per_step": OPS_PER_STEP,
+            "config": {"workload": WORKLOAD, "m": m, "ops_per_step": OPS_PER_STEP, "w4a4_path": args.w4a4_path,
                        "parallelism": "single GPU" if world == 1 else f"N-sharded x{world} + all-gather",
                        "outputs": "fp16", "l2": f"per-step working set {working_set / 1e6:.0f} MB per GPU exceeds the 126 MB L2"},
             "gpu_launches": timed_launches,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "roofline": {"kernel": "w4a4_wide::gemm_kernel", "bound": "tensor", "achieved": achieved, "peak": int8_peak,
+            "roofline": {"kernel": "w4a4::gemm_kernel" if args.w4a4_path == "packed" else "w4a4_pair::gemm_kernel", "bound": "tensor", "achieved": achieved, "peak": int8_peak,
                          "unit": "TOP/s", "frac": achieved / int8_peak, "traffic": None,
                          "peak_source": f"2 x the sustained bf16 figure of MEASURED_PEAKS.json ({peaks['source']}); "
                                         "no 8-bit figure is measured; fp8 and int8 run at twice the bf16 rate",
@@ -371,6 +380,9 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    parser.add_argument("--w4a4-path", default="packed", choices=["packed", "wide"],
+                        help="packed: the drop-in kernels on nibble-packed codes (int8 tensor-core dots); "
+                             "wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

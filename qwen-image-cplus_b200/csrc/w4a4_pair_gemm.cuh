@@ -121,7 +121,7 @@ __device__ __forceinline__ void fold_role(const View &v, const __half *__restric
     const uint32_t tmem_lane = v.tmem_base + slice * COLUMNS + (static_cast<uint32_t>(quadrant * 32) << 16);
     const int my_tiles = v.pair < v.tiles ? (v.tiles - 1 - v.pair) / v.pairs + 1 : 0;
     const uint32_t total_groups = static_cast<uint32_t>(my_tiles) * v.groups;
-    uint32_t set[DOUBLE_BUFFER ? 2 : 1][32];  // [16 * half + 4 * x + 2 * a + e]: rows fragment_row + 16 half + 8 a, columns 8 x + pair_column + e
+    uint32_t set[DOUBLE_BUFFER ? 2 : 1][32] = {};  // [16 * half + 4 * x + 2 * a + e]: rows fragment_row + 16 half + 8 a, columns 8 x + pair_column + e
     bool alive = true;
 
     // Starts the load of batch `batch` of group `group_count`; the first batch of a group waits for its dots.
@@ -139,6 +139,7 @@ __device__ __forceinline__ void fold_role(const View &v, const __half *__restric
             tcgen05_fence_after();
         }
         const uint32_t address = tmem_lane + buffer * BN + batch * 32;
+        if (shape.ablate & 8) return true;  // tuning: leave the registers as they are
         tmem_load_16x256_x4(address, &destination[0]);
         tmem_load_16x256_x4(address + (16u << 16), &destination[16]);
         return true;
@@ -218,15 +219,18 @@ __device__ __forceinline__ void fold_role(const View &v, const __half *__restric
                     if (!(shape.ablate & 2)) {
 #pragma unroll
                         for (int x = 0; x < 4; ++x) {
-                            // scalar on purpose: measured on this chip, the compiler's code for packed
-                            // mul/fma.f32x2 here ran four times slower than plain FMUL + FFMA
+                            // scalar FMUL + FFMA: as fast on the fp32 pipe as the packed f32x2 forms and free of
+                            // their 64-bit register-pair constraints; the eight scale products come first
                             const float2 sw = *reinterpret_cast<const float2 *>(sw_group + b * 32 + 8 * x);
+                            float product[4][2];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) product[i][0] = sa[i] * sw.x, product[i][1] = sa[i] * sw.y;
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 const int r = 16 * (i >> 1) + 4 * x + 2 * (i & 1);
                                 const int c = 2 * (b * 4 + x);
-                                acc[i][c] = fmaf(__uint_as_float(current[r]), sa[i] * sw.x, acc[i][c]);
-                                acc[i][c + 1] = fmaf(__uint_as_float(current[r + 1]), sa[i] * sw.y, acc[i][c + 1]);
+                                acc[i][c] = fmaf(__uint_as_float(current[r]), product[i][0], acc[i][c]);
+                                acc[i][c + 1] = fmaf(__uint_as_float(current[r + 1]), product[i][1], acc[i][c + 1]);
                             }
                         }
                     }
