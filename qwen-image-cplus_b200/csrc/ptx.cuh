@@ -84,11 +84,19 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint64_t *barrier, uint32_t pa
 }
 
 // Bounded wait. On time-out writes `code` to *status (first writer wins) and returns false;
-// also returns false as soon as another thread of the grid has recorded a failure.
-__device__ __forceinline__ bool mbarrier_wait(uint64_t *barrier, uint32_t parity, uint32_t *status,
-                                              uint32_t code) {
-    for (uint32_t spin = 0; spin < WAIT_FAST_SPINS; ++spin)
+// also gives up as soon as another thread has reported a failure. The caller must then drain
+// and leave without touching the data.
+// A wait whose phase is already complete is the common case in a pipeline that runs ahead, and it
+// must cost no more than the one try_wait (about 25 cycles; a loop around it triples that).
+__device__ __forceinline__ bool mbarrier_wait_spin(uint64_t *barrier, uint32_t parity, uint32_t *status, uint32_t code,
+                                                   uint32_t backoff_ns = 0) {
+    for (uint32_t spin = 0; spin < WAIT_FAST_SPINS; ++spin) {
         if (mbarrier_try_wait(barrier, parity)) return true;
+        // A role that runs far ahead of its consumers spends its life here. Without a pause its polling
+        // takes issue slots from the warps that share its scheduler (measured: a fold warp next to a
+        // spinning warp fell four groups behind the others and set the pace of the whole CTA).
+        if (backoff_ns != 0) __nanosleep(backoff_ns);
+    }
     const uint64_t start = global_timer_ns();
     while (true) {
         if (mbarrier_try_wait(barrier, parity)) return true;
@@ -100,12 +108,20 @@ __device__ __forceinline__ bool mbarrier_wait(uint64_t *barrier, uint32_t parity
     return false;
 }
 
-// The same for a whole converged warp: lane 0 polls, the others wait for it at a warp barrier
-// (32 lanes polling one barrier word only multiply the shared-memory traffic).
+__device__ __forceinline__ bool mbarrier_wait(uint64_t *barrier, uint32_t parity, uint32_t *status,
+                                              uint32_t code, uint32_t backoff_ns = 0) {
+    if (mbarrier_try_wait(barrier, parity)) return true;
+    return mbarrier_wait_spin(barrier, parity, status, code, backoff_ns);
+}
+
+// The same for a whole converged warp. Every lane makes the first attempt (one instruction, one
+// shared-memory access for the warp). Only if that fails does lane 0 poll alone while the others
+// wait for it at a shuffle: 32 lanes spinning on one barrier word only multiply the traffic.
 __device__ __forceinline__ bool mbarrier_wait_warp(uint64_t *barrier, uint32_t parity, uint32_t *status,
-                                                   uint32_t code, int lane) {
+                                                   uint32_t code, int lane, uint32_t backoff_ns = 0) {
+    if (__all_sync(0xffffffffu, mbarrier_try_wait(barrier, parity))) return true;
     uint32_t ok = 1;
-    if (lane == 0) ok = mbarrier_wait(barrier, parity, status, code) ? 1u : 0u;
+    if (lane == 0) ok = mbarrier_wait_spin(barrier, parity, status, code, backoff_ns) ? 1u : 0u;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
@@ -416,6 +432,14 @@ __device__ __forceinline__ void tmem_load_32x16(uint32_t address, uint32_t (&r)[
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(address)
         : "memory");
+}
+
+// 32-byte store (sm_100): a thread that owns 32 adjacent bytes of a row writes a whole sector at once.
+// The address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void *address, const uint32_t (&r)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
 }
 
 // ---- small utilities -----------------------------------------------------------------------

@@ -199,7 +199,7 @@ int launch_w4a4_pair(const void *a_bytes, const void *a_scales, const void *w_by
                   wp::STAGE_K, wp::BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return INVALID;
     if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_bytes, shape.k, shape.n, static_cast<uint64_t>(shape.k),
-                  wp::STAGE_K, wp::BN / 2, CU_TENSOR_MAP_SWIZZLE_128B))
+                  wp::STAGE_K, wp::B_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B))
         return INVALID;
     auto kernel = dots != nullptr ? wp::gemm_kernel<true> : wp::gemm_kernel<false>;
     static bool configured[MAX_DEVICES][2];

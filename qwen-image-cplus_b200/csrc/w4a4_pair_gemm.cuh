@@ -1,20 +1,40 @@
-// W4A4 (H256, g64) GEMM on byte-wide (E4M3) codes, one 256 x 256 output tile per PAIR of CTAs
+// W4A4 (H256, g64) GEMM on byte-wide (E4M3) codes, one 256 x 128 output tile per PAIR of CTAs
 // (thread-block cluster of two, tcgen05 cta_group::2). Same operator, arithmetic and bits as
 // w4a4_wide_gemm.cuh and the reference's w4a4_gemm_kernel (qwen_image_cuda/cuda/gemm.cu:65-189).
 //
-// Why pairs: with one byte per code a 128 x 128 tile moves 32 KB from L2 per 2.1 M multiply-adds,
-// and the L2 -> SM path (about 8 TB/s over the chip) saturates long before the tensor cores do.
-// In a pair each CTA loads its own 128 rows of A and only HALF of the tile's B rows; the MMA
-// (M = 256 across the pair, N = 256) reads both halves of B from both CTAs' shared memory. That is
-// 32 KB per 4.2 M multiply-adds per CTA: half the traffic, with no TMA multicast.
+// Per group of 64 inputs the tensor cores leave a tile of EXACT integer dots (as fp32) in TMEM and
+// the fp32 pipe folds them: y += dot * (sa * sw). That fold is two fp32 operations per output and
+// group - at full tensor rate more than the fp32 pipe can do - so the kernel is built around
+// keeping sixteen fold warps busy and everything else out of their way. What was measured on the
+// way, and what the design does about it:
 //
-// Per CTA (rank 0 = leader issues the MMAs for both):
-//   warp 0      TMA: own A rows and own half of B; completion bytes are counted on the leader's barrier
-//   warp 1      leader only: per group two tcgen05.mma.cta_group::2 kind::f8f6f4 (K = 32) into one of
-//               two TMEM buffers of 256 fp32 columns; commits arrive on both CTAs' barriers
-//   warps 2-3   stage sw of the stage's two groups (256 columns) as fp32
-//   warps 4-11  fold this CTA's 128 rows x 256 columns, 32 rows x 128 columns per warp; after its last
-//               load of a group the warp releases the TMEM buffer on the LEADER's barrier
+//   * In a pair each CTA loads its own 128 rows of A and HALF of the B rows; the MMAs (M = 256
+//     across the pair) read B from both CTAs' shared memory. No TMA multicast.
+//   * Warps that wait on the same barrier run in lock step: all copy dots out of TMEM at the same
+//     time (queueing at the TMEM read port), then all multiply at the same time. So the tile's 128
+//     columns are split into two TEAMS of 64, each a pipeline of its own: own MMAs (N = 64), own
+//     four TMEM buffers, own barriers, own eight fold warps per CTA. The teams drift apart and one
+//     fills the other's gaps.
+//   * A tcgen05.commit holds up the later tcgen05 instructions of the THREAD that issued it for
+//     some 440 cycles, however deep the pipeline, but not those of other threads. So each team has
+//     two issuing threads (in different warps) that take turns group by group.
+//   * A fold warp copies its 32 x 32 dots of a group with one tcgen05.ld.32x32b.x32 (about 360
+//     B/clk/SM with eight warps; the 16x256b fragment shape reaches 230), hands the buffer back
+//     at once and then does the arithmetic from registers.
+//   * A wait on a barrier whose phase is complete must cost one try_wait (25 cycles). A polling
+//     loop with a lane-0 / shuffle wrapper around it cost 230, several times per group.
+//   * Integer division costs a warp over a hundred cycles: the per-stage roles walk the
+//     (tile, stage) sequence incrementally. Scales reach the fold threads as fp32 in shared memory,
+//     staged by one warp with cp.async several stages ahead; that warp also issues the TMA.
+//   * A thread owns one output row: it stores whole 32-byte sectors (st.global.v8).
+//
+// Per CTA (rank 0 = leader issues the MMAs for both), 24 warps:
+//   warp 0      stage the scales (sa: this CTA's 128 rows, sw: the tile's 128 columns, two groups
+//               per stage) and issue the TMA for own A rows and own B rows
+//   warps 4-7   leader only, one thread each: tcgen05.mma.cta_group::2 kind::f8f6f4 (two K = 32 steps
+//               per group) and the commit that arrives on both CTAs' barriers
+//   warps 8-23  fold this CTA's 128 rows x 128 columns, 32 rows x 32 columns per warp
+//   (warps 1-3 only give up their registers: setmaxnreg works on groups of four warps)
 #pragma once
 #include "ptx.cuh"
 #include "w4a16_gemm.cuh"
@@ -22,251 +42,280 @@
 namespace qi {
 namespace w4a4_pair {
 
-constexpr int THREADS = 384;
+constexpr int TEAMS = 2;       // independent fold pipelines, each with its own half of the columns
+constexpr int THREADS = 768;
 constexpr int BM = 128;        // rows per CTA; the pair covers 256
-constexpr int BN = 256;        // columns of the pair's tile; each CTA loads 128 of the B rows
-constexpr int STAGE_K = 128;
-constexpr int BUFFERS = 2;     // TMEM buffers of BN fp32 columns
-constexpr int STAGES = 6;
-constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, SCALE_WARP0 = 2, SCALE_WARPS = 2, FOLD_WARP0 = 4, FOLD_WARPS = 8;
-constexpr int COLUMNS = BN / (FOLD_WARPS / 4);  // columns per fold warp: 128
-constexpr bool DOUBLE_BUFFER = true;            // a second register set for the dots in flight
-// setmaxnreg can only hand out what the launch allocated: floor8(65536 / 384) = 168 registers per thread.
-// Two fold warps per scheduler, each with 128 accumulators and two sets of 32 fetched dots. Measured
-// against four warps per scheduler with 64 accumulators and one set (112 registers, spills): 1.7x faster.
-constexpr int LAUNCH_REGISTERS = 168, CONTROL_REGISTERS = 40, FOLD_REGISTERS = 232;
-static_assert(128 * CONTROL_REGISTERS + FOLD_WARPS * 32 * FOLD_REGISTERS <= THREADS * LAUNCH_REGISTERS,
+constexpr int BN = 128;        // columns of the pair's tile; each CTA loads 64 of the B rows
+constexpr int STAGE_K = 128;   // bytes (= codes) of K per pipeline stage: two groups
+constexpr int TEAM_COLUMNS = BN / TEAMS;
+constexpr int BUFFERS = 4;     // TMEM buffers of TEAM_COLUMNS fp32 columns per team
+constexpr int STAGES = 8;
+constexpr int TURNS = 2;       // MMA-issuing threads per team, taking turns group by group
+constexpr int STAGING_WARP = 0, MMA_WARP0 = 4, MMA_WARPS = TURNS * TEAMS, FOLD_WARP0 = 8, FOLD_WARPS = 16;  // warps 1-3 idle
+static_assert(MMA_WARP0 + MMA_WARPS <= FOLD_WARP0, "the issuing threads sit in control warps");
+constexpr int COLUMNS = BN / (FOLD_WARPS / 4);  // columns per fold warp: 32
+// Registers live in the four schedulers' own files (16384 each), and warp w runs on scheduler w % 4:
+// six warps per scheduler here, 80 registers per thread at launch. setmaxnreg moves registers
+// between the warps of ONE scheduler, and it is executed by whole warpgroups (four consecutive
+// warps) - hence eight control warps although three of them have nothing to do. Per scheduler
+// afterwards: two control warps and four fold warps.
+// A fold thread keeps 32 accumulators and 32 fetched dots.
+constexpr int LAUNCH_REGISTERS = 80, CONTROL_REGISTERS = 48, FOLD_REGISTERS = 96;
+static_assert(THREADS % 128 == 0 && FOLD_WARP0 % 4 == 0, "setmaxnreg is a warpgroup instruction");
+static_assert(THREADS / 128 * LAUNCH_REGISTERS * 32 <= 16384, "registers of one scheduler at launch");
+static_assert(FOLD_WARP0 / 4 * CONTROL_REGISTERS + FOLD_WARPS / 4 * FOLD_REGISTERS <= THREADS / 128 * LAUNCH_REGISTERS,
               "setmaxnreg.inc would wait for registers that do not exist");
-constexpr int SCALE_AHEAD = 6, SCALE_RING = 8;
+constexpr int SCALE_AHEAD = 6, SCALE_RING = 8;  // stages of scales in flight; ring slots
 
 constexpr int A_BYTES = BM * 128, B_BYTES = (BN / 2) * 128;
-constexpr int SCALE_BYTES = 2 * BN * 4;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SCALE_BYTES;
-constexpr int RING_BYTES = SCALE_RING * BN * 4;
+constexpr int SW_BYTES = 2 * BN * 4;   // fp32 [group of the stage][column]
+constexpr int SA_BYTES = BM * 8;       // float2 [row] = (group 0, group 1)
+constexpr int RING_BYTES = SCALE_RING * (BN + BM) * 4;  // half2 per column / row and slot
 constexpr int BARRIER_BYTES = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RING_BYTES + BARRIER_BYTES + 1024;
+constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES + SW_BYTES + SA_BYTES) + RING_BYTES + BARRIER_BYTES + 1024;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
-static_assert((3 * STAGES + 2 * BUFFERS) * 8 + 8 <= BARRIER_BYTES, "barrier block");
-
+static_assert((3 * STAGES + 2 * TEAMS * BUFFERS) * 8 + 8 <= BARRIER_BYTES, "barrier block");
+constexpr int B_BOX_ROWS = TEAM_COLUMNS / 2;  // rows of B per TMA load: one CTA's half of one team's columns
+static_assert(BN == 128 && BM == 128, "the staging warp handles four columns and four rows per lane");
 
 // Everything a role needs to find its way around the CTA's shared memory and the problem.
 struct View {
+    uint8_t *tile_a, *tile_b;
     float *sw_tile;
-    __half2 *sw_ring;
-    uint64_t *scale_ready, *empty, *dot_full, *dot_empty;
+    float2 *sa_tile;
+    __half2 *ring;
+    uint64_t *full, *scale_ready, *empty, *dot_full, *dot_empty;
     uint32_t tmem_base, cta;
     int pair, pairs, tiles, tiles_m, k_stages, groups;
 };
 
-// Warps 2-3: weight scales of each stage's two groups for the tile's 256 columns, converted to fp32
-// once for all fold threads; fetched SCALE_AHEAD stages early with cp.async (one global-load latency
-// is longer than the tensor core needs for a stage).
-__device__ __forceinline__ void scale_role(const View &v, const __half *__restrict__ w_scales, const GemmShape &shape,
-                                           int t, int lane) {
-    const int my_tiles = v.pair < v.tiles ? (v.tiles - 1 - v.pair) / v.pairs + 1 : 0;
-    const uint32_t total = static_cast<uint32_t>(my_tiles) * v.k_stages;
-    auto fetch = [&](uint32_t it) {
-        if (it < total) {
-            const int tile = v.pair + static_cast<int>(it / v.k_stages) * v.pairs;
-            const int ks = it % v.k_stages, n0 = (tile / v.tiles_m) * BN;
-#pragma unroll
-            for (int p = 0; p < BN / 64; ++p) {
-                const int col = n0 + p * 64 + t;
-                __half2 *slot = v.sw_ring + (it % SCALE_RING) * BN + p * 64 + t;
-                if (col < shape.n) cp_async_4(slot, w_scales + static_cast<size_t>(col) * v.groups + 2 * ks);
-                else *slot = __halves2half2(__ushort_as_half(0), __ushort_as_half(0));
+// A walk over this pair's (tile, stage) sequence without divisions in the loop: integer division
+// costs a warp more than a hundred cycles, and a role that pays several per stage becomes the
+// pace-setter of the whole kernel.
+struct StageWalk {
+    int tile, ks, m_index, n_index;
+    __device__ __forceinline__ StageWalk(const View &v) : tile(v.pair), ks(0), m_index(v.pair % v.tiles_m), n_index(v.pair / v.tiles_m) {}
+    __device__ __forceinline__ bool done(const View &v) const { return tile >= v.tiles; }
+    __device__ __forceinline__ void next(const View &v) {
+        if (++ks == v.k_stages) {
+            ks = 0;
+            tile += v.pairs;
+            m_index += v.pairs;  // pairs may exceed tiles_m: reduce by repeated subtraction of the few wraps
+            while (m_index >= v.tiles_m) {
+                m_index -= v.tiles_m;
+                ++n_index;
             }
         }
+    }
+};
+
+// Warp 0. Per stage: fetch the two groups' scales (one half2 per column and per row) SCALE_AHEAD
+// stages early with 4-byte cp.async; when the stage's buffers are free again, lane 0 starts the TMA
+// of this CTA's A rows and B rows and the warp writes the scales out as fp32: sw[group][column]
+// and sa[row] = (group 0, group 1).
+__device__ __forceinline__ void staging_role(const View &v, const CUtensorMap *map_a, const CUtensorMap *map_w,
+                                             const __half *__restrict__ a_scales, const __half *__restrict__ w_scales,
+                                             const GemmShape &shape, int lane) {
+    if (lane == 0) {
+        prefetch_tensormap(map_a);
+        prefetch_tensormap(map_w);
+    }
+    StageWalk ahead(v);
+    uint32_t ahead_slot = 0;
+    auto fetch = [&]() {
+        if (!ahead.done(v)) {
+            const int n0 = ahead.n_index * BN, m0 = ahead.m_index * 2 * BM + static_cast<int>(v.cta) * BM;
+            __half2 *slot = v.ring + ahead_slot * (BN + BM) + lane;
+            const __half *w_source = w_scales + static_cast<size_t>(n0 + lane) * v.groups + 2 * ahead.ks;
+            const __half *a_source = a_scales + static_cast<size_t>(m0 + lane) * v.groups + 2 * ahead.ks;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                if (n0 + p * 32 + lane < shape.n) cp_async_4(slot + p * 32, w_source + static_cast<size_t>(p * 32) * v.groups);
+                else slot[p * 32] = __halves2half2(__ushort_as_half(0), __ushort_as_half(0));
+                if (m0 + p * 32 + lane < shape.m) cp_async_4(slot + BN + p * 32, a_source + static_cast<size_t>(p * 32) * v.groups);
+                else slot[BN + p * 32] = __halves2half2(__ushort_as_half(0), __ushort_as_half(0));
+            }
+            ahead.next(v);
+        }
+        if (++ahead_slot == SCALE_RING) ahead_slot = 0;
         cp_async_commit();
     };
-    for (uint32_t it = 0; it < SCALE_AHEAD; ++it) fetch(it);
-    for (uint32_t it = 0; it < total; ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        fetch(it + SCALE_AHEAD);
-        cp_async_wait<SCALE_AHEAD>();  // this thread's copies for stage `it` have landed
-        float2 values[BN / 64];
+    for (int i = 0; i < SCALE_AHEAD; ++i) fetch();
+    uint32_t s = 0, phase = 0, slot_index = 0;
+    for (StageWalk walk(v); !walk.done(v); walk.next(v)) {
+        fetch();
+        cp_async_wait<SCALE_AHEAD>();  // this thread's copies for this stage have landed
+        const __half2 *slot = v.ring + slot_index * (BN + BM) + lane;
+        float2 sw[4], sa[4];
 #pragma unroll
-        for (int p = 0; p < BN / 64; ++p) values[p] = __half22float2(v.sw_ring[(it % SCALE_RING) * BN + p * 64 + t]);
+        for (int p = 0; p < 4; ++p) {
+            sw[p] = __half22float2(slot[p * 32]);
+            sa[p] = __half22float2(slot[BN + p * 32]);
+        }
         if (!mbarrier_wait_warp(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x6000 | s, lane)) break;
-        float *sw_stage = v.sw_tile + s * 2 * BN;
+        if (lane == 0) {
+            const int m0 = walk.m_index * 2 * BM + static_cast<int>(v.cta) * BM;
+            const int n0 = walk.n_index * BN + static_cast<int>(v.cta) * B_BOX_ROWS;
+            // the leader expects the bytes of both CTAs' loads on its barrier
+            if (v.cta == 0) mbarrier_arrive_expect_tx(&v.full[s], 2 * (A_BYTES + B_BYTES));
+            tma_load_2d_pair(v.tile_a + s * A_BYTES, map_a, &v.full[s], walk.ks * STAGE_K, m0);
 #pragma unroll
-        for (int p = 0; p < BN / 64; ++p) {
-            sw_stage[p * 64 + t] = values[p].x;
-            sw_stage[BN + p * 64 + t] = values[p].y;
+            for (int team = 0; team < TEAMS; ++team)  // this CTA's half of each team's columns
+                tma_load_2d_pair(v.tile_b + s * B_BYTES + team * (B_BOX_ROWS * 128), map_w, &v.full[s], walk.ks * STAGE_K,
+                                 n0 + team * TEAM_COLUMNS);
+        }
+        float *sw_stage = v.sw_tile + s * 2 * BN + lane;
+        float2 *sa_stage = v.sa_tile + s * BM + lane;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            sw_stage[p * 32] = sw[p].x;
+            sw_stage[BN + p * 32] = sw[p].y;
+            sa_stage[p * 32] = sa[p];
         }
         __syncwarp();
         if (lane == 0) mbarrier_arrive(&v.scale_ready[s]);
+        if (++s == STAGES) s = 0, phase ^= 1;
+        if (++slot_index == SCALE_RING) slot_index = 0;
     }
     cp_async_wait<0>();
 }
 
-// Warps 4-11: a warp folds 32 rows x 128 columns of this CTA's half of the tile.
-// The dots are fetched with tcgen05.ld.16x256b, whose register layout is that of an MMA accumulator
-// fragment: a thread holds 4 rows x 32 columns (column pairs 8 apart), not 1 row x 128 columns.
-// With a whole row per thread every lane needs the SAME weight scale for a column, i.e. one
-// shared-memory broadcast per column and warp - more load wavefronts than the fp32 pipe has
-// cycles. In the fragment layout a thread's columns never change, so a group costs 16 eight-byte
-// loads of sw and 4 values of sa per thread.
-// With DOUBLE_BUFFER two register sets alternate (the tcgen05.ld of the next 32-column batch is in flight
-// during the arithmetic of this one).
-template <bool DUMP_DOTS>
-__device__ __forceinline__ void fold_role(const View &v, const __half *__restrict__ a_scales,
-                                          const float *__restrict__ bias, void *__restrict__ y,
-                                          int32_t *__restrict__ dots_out, const GemmShape &shape, int warp, int lane) {
-    constexpr int BATCHES = COLUMNS / 32;  // 4 per group
-    const int quadrant = warp & 3, slice = (warp - FOLD_WARP0) >> 2;
-    const int pair_column = 2 * (lane & 3), fragment_row = lane >> 2;
-    const uint32_t leader_dot_empty = map_to_cta(smem_u32(v.dot_empty), 0);
-    const uint32_t tmem_lane = v.tmem_base + slice * COLUMNS + (static_cast<uint32_t>(quadrant * 32) << 16);
+// Warps 4-7 of the leader, one thread each. Thread `mine` serves team (mine % TEAMS) and multiplies the
+// groups whose running number is (mine / TEAMS) modulo TURNS into that team's TMEM buffers: N = 64
+// columns per MMA. A group's number fixes everything else: its pipeline stage (two groups per stage) and
+// its buffer.
+__device__ __forceinline__ void mma_role(const View &v, uint32_t mine) {
+    constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * BM, TEAM_COLUMNS);
     const int my_tiles = v.pair < v.tiles ? (v.tiles - 1 - v.pair) / v.pairs + 1 : 0;
     const uint32_t total_groups = static_cast<uint32_t>(my_tiles) * v.groups;
-    uint32_t set[DOUBLE_BUFFER ? 2 : 1][32] = {};  // [16 * half + 4 * x + 2 * a + e]: rows fragment_row + 16 half + 8 a, columns 8 x + pair_column + e
+    const uint32_t team = mine % TEAMS, turn = mine / TEAMS;
+    uint64_t *dot_full = v.dot_full + team * BUFFERS, *dot_empty = v.dot_empty + team * BUFFERS;
+    for (uint32_t group = turn; group < total_groups; group += TURNS) {
+        const uint32_t iteration = group >> 1, gl = group & 1;
+        const uint32_t s = iteration % STAGES, phase = (iteration / STAGES) & 1;
+        const uint32_t buffer = group % BUFFERS, buffer_phase = (group / BUFFERS) & 1;
+        if (!mbarrier_wait(&v.full[s], phase, &g_status, STATUS_WAIT_FULL | 0x5000 | s)) break;
+        if (!mbarrier_wait(&dot_empty[buffer], buffer_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x5000 | buffer)) break;
+        tcgen05_fence_after();
+        const uint32_t a_address = smem_u32(v.tile_a + s * A_BYTES) + gl * 64;
+        const uint32_t b_address = smem_u32(v.tile_b + s * B_BYTES + team * (B_BOX_ROWS * 128)) + gl * 64;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk)
+            umma_f8_pair(v.tmem_base + (team * BUFFERS + buffer) * TEAM_COLUMNS, umma_desc_k_sw128(a_address + kk * 32),
+                         umma_desc_k_sw128(b_address + kk * 32), idesc, kk);
+        tcgen05_commit_pair(&dot_full[buffer]);
+    }
+}
+
+// Warps 8-23: a warp folds 32 rows x 32 columns of this CTA's half of the tile; a thread owns one
+// row (its TMEM lane) and 32 accumulators.
+// Per group a warp waits for the dots, copies its 32 x 32 of them into registers with one
+// tcgen05.ld.32x32b.x32 (the shape with the highest TMEM read rate), hands the buffer back and
+// then does the arithmetic; the other three warps of its scheduler fill the waits.
+// All lanes need the same weight scales: one 16-byte broadcast load per four columns.
+// The arithmetic is the packed fp32 pair form of  acc = fma(dot, sa * sw, acc): each half is
+// IEEE-rounded exactly like the scalar instruction, so the result has the reference's bits.
+template <bool DUMP_DOTS>
+__device__ __forceinline__ void fold_role(const View &v, const float *__restrict__ bias, void *__restrict__ y,
+                                          int32_t *__restrict__ dots_out, const GemmShape &shape, int warp, int lane) {
+    static_assert(COLUMNS == 32, "one tcgen05.ld.32x32b.x32 per warp and group");
+    // The hardware ties a warp to the TMEM lanes 32 * (warp % 4); four consecutive warps make one column slice.
+    const int quadrant = warp & 3, slice = (warp - FOLD_WARP0) >> 2, team = slice / (TEAM_COLUMNS / COLUMNS);
+    const uint64_t *dot_full = v.dot_full + team * BUFFERS;
+    const uint32_t leader_dot_empty = map_to_cta(smem_u32(v.dot_empty + team * BUFFERS), 0);
+    const uint32_t tmem_lane = v.tmem_base + team * BUFFERS * TEAM_COLUMNS + (slice % (TEAM_COLUMNS / COLUMNS)) * COLUMNS +
+                               (static_cast<uint32_t>(quadrant * 32) << 16);
+    uint32_t dots[COLUMNS];  // dots[j] = dot of this thread's row and column j of the warp's 32
     bool alive = true;
-
-    // Starts the load of batch `batch` of group `group_count`; the first batch of a group waits for its dots.
-    auto issue = [&](uint32_t group_count, int batch, uint32_t (&destination)[32], bool blocking) -> bool {
-        const uint32_t buffer = group_count % BUFFERS, phase = (group_count / BUFFERS) & 1;
-        if (batch == 0) {
-            if (!blocking) {
-                uint32_t ready = 0;
-                if (lane == 0) ready = mbarrier_try_wait(&v.dot_full[buffer], phase) ? 1u : 0u;
-                if (__shfl_sync(0xffffffffu, ready, 0) == 0) return false;
-            } else if (!mbarrier_wait_warp(&v.dot_full[buffer], phase, &g_status, STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane)) {
-                alive = false;
-                return false;
-            }
-            tcgen05_fence_after();
-        }
-        const uint32_t address = tmem_lane + buffer * BN + batch * 32;
-        if (shape.ablate & 8) return true;  // tuning: leave the registers as they are
-        tmem_load_16x256_x4(address, &destination[0]);
-        tmem_load_16x256_x4(address + (16u << 16), &destination[16]);
-        return true;
-    };
-
     uint32_t iteration = 0, group_count = 0;
-    if (total_groups > 0) issue(0, 0, set[0], true);
     for (int tile = v.pair; tile < v.tiles && alive; tile += v.pairs) {
-        const int m0 = (tile % v.tiles_m) * 2 * BM + v.cta * BM + quadrant * 32, n0 = (tile / v.tiles_m) * BN + slice * COLUMNS;
-        // this thread's four rows: m0 + fragment_row + 8 * index, index = 2 * half + a
-        const __half *sa_rows[4];
+        const int row = (tile % v.tiles_m) * 2 * BM + static_cast<int>(v.cta) * BM + quadrant * 32 + lane;
+        const int n0 = (tile / v.tiles_m) * BN + slice * COLUMNS;
+        uint64_t acc[COLUMNS / 2];  // acc[j] = columns 2 j, 2 j + 1
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int row = m0 + fragment_row + 8 * i;
-            sa_rows[i] = a_scales + static_cast<size_t>(row < shape.m ? row : 0) * v.groups;
-        }
-        float acc[4][COLUMNS / 4];  // [row index][2 * column pair + element]
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < COLUMNS / 4; ++j) acc[i][j] = 0.0f;
-        __half2 sa_next[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sa_next[i] = __ldg(reinterpret_cast<const __half2 *>(sa_rows[i]));
+        for (int j = 0; j < COLUMNS / 2; ++j) acc[j] = 0;
         for (int ks = 0; ks < v.k_stages && alive; ++ks, ++iteration) {
             const int s = iteration % STAGES;
             const uint32_t phase = (iteration / STAGES) & 1;
-            float2 sa_pair[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                sa_pair[i] = __half22float2(sa_next[i]);
-                if (ks + 1 < v.k_stages) sa_next[i] = __ldg(reinterpret_cast<const __half2 *>(sa_rows[i] + 2 * ks + 2));
-            }
             if (!mbarrier_wait_warp(&v.scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x5000 | s, lane)) { alive = false; break; }
-            const float *sw_stage = v.sw_tile + s * 2 * BN + slice * COLUMNS + pair_column;
+            const float *sw_stage = v.sw_tile + s * 2 * BN + slice * COLUMNS;
+            const float2 sa_pair = v.sa_tile[s * BM + quadrant * 32 + lane];
 #pragma unroll
             for (int gl = 0; gl < 2; ++gl, ++group_count) {
                 const uint32_t buffer = group_count % BUFFERS;
-                float sa[4];
+                if (!mbarrier_wait_warp(const_cast<uint64_t *>(&dot_full[buffer]), (group_count / BUFFERS) & 1, &g_status,
+                                        STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane)) { alive = false; break; }
+                tcgen05_fence_after();
+                tmem_load_32x32(tmem_lane + buffer * TEAM_COLUMNS, dots);
+                tmem_load_wait();
+                // this warp's share of the buffer is in registers: hand it back to the leader's MMA threads
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbarrier_arrive_cluster(leader_dot_empty + buffer * 8);
+                if (DUMP_DOTS && row < shape.m) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) sa[i] = gl == 0 ? sa_pair[i].x : sa_pair[i].y;
+                    for (int j = 0; j < COLUMNS; ++j)
+                        if (n0 + j < shape.n)
+                            dots_out[(static_cast<size_t>(row) * shape.n + n0 + j) * v.groups + ks * 2 + gl] =
+                                static_cast<int32_t>(__uint_as_float(dots[j]));
+                }
+                const float scale = gl == 0 ? sa_pair.x : sa_pair.y;
+                const uint64_t sa2 = pack_f32x2(scale, scale);
                 const float *sw_group = sw_stage + gl * BN;
 #pragma unroll
-                for (int b = 0; b < BATCHES; ++b) {
-                    uint32_t(&current)[32] = set[DOUBLE_BUFFER ? (b & 1) : 0];
-                    uint32_t(&following)[32] = set[DOUBLE_BUFFER ? ((b + 1) & 1) : 0];
-                    tmem_load_wait();  // `current` has landed; nothing else is in flight
-                    const bool last_batch = b == BATCHES - 1;
-                    const uint32_t next_group = group_count + (last_batch ? 1 : 0);
-                    const bool has_next = next_group < total_groups;
-                    bool issued = false;
-                    if (last_batch) {
-                        // every dot of this buffer is in registers: hand it back to the leader's MMA thread
-                        tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbarrier_arrive_cluster(leader_dot_empty + buffer * 8);
-                        if (DOUBLE_BUFFER && has_next) issued = issue(next_group, 0, following, false);  // only if its dots are already there
-                    } else if (DOUBLE_BUFFER) {
-                        issued = issue(group_count, b + 1, following, true);
-                    }
-                    if (DUMP_DOTS) {
-                        const int group = ks * 2 + gl;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int row = m0 + fragment_row + 8 * i;
-#pragma unroll
-                            for (int x = 0; x < 4; ++x)
-#pragma unroll
-                                for (int e = 0; e < 2; ++e) {
-                                    const int col = n0 + b * 32 + 8 * x + pair_column + e;
-                                    if (row < shape.m && col < shape.n)
-                                        dots_out[(static_cast<size_t>(row) * shape.n + col) * v.groups + group] =
-                                            static_cast<int32_t>(__uint_as_float(current[16 * (i >> 1) + 4 * x + 2 * (i & 1) + e]));
-                                }
-                        }
-                    }
-                    if (!(shape.ablate & 2)) {
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) {
-                            // scalar FMUL + FFMA: as fast on the fp32 pipe as the packed f32x2 forms and free of
-                            // their 64-bit register-pair constraints; the eight scale products come first
-                            const float2 sw = *reinterpret_cast<const float2 *>(sw_group + b * 32 + 8 * x);
-                            float product[4][2];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) product[i][0] = sa[i] * sw.x, product[i][1] = sa[i] * sw.y;
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int r = 16 * (i >> 1) + 4 * x + 2 * (i & 1);
-                                const int c = 2 * (b * 4 + x);
-                                acc[i][c] = fmaf(__uint_as_float(current[r]), product[i][0], acc[i][c]);
-                                acc[i][c + 1] = fmaf(__uint_as_float(current[r + 1]), product[i][1], acc[i][c + 1]);
-                            }
-                        }
-                    }
-                    if (last_batch) {
-                        if (has_next && !issued && alive) issue(next_group, 0, following, true);
-                    } else if (!DOUBLE_BUFFER) {
-                        issue(group_count, b + 1, following, true);
-                    }
+                for (int q = 0; q < COLUMNS / 4; ++q) {
+                    const ulonglong2 sw4 = *reinterpret_cast<const ulonglong2 *>(sw_group + 4 * q);  // four columns, as two pairs
+                    acc[2 * q] = fma_f32x2(pack_u32x2(dots[4 * q], dots[4 * q + 1]), mul_f32x2(sa2, sw4.x), acc[2 * q]);
+                    acc[2 * q + 1] = fma_f32x2(pack_u32x2(dots[4 * q + 2], dots[4 * q + 3]), mul_f32x2(sa2, sw4.y), acc[2 * q + 1]);
                 }
-                if (!alive) break;
             }
             if (alive) {
                 __syncwarp();
-                if (lane == 0) mbarrier_arrive(&v.empty[s]);  // done reading this stage's sw
+                if (lane == 0) mbarrier_arrive(&v.empty[s]);  // done with this stage's scales; its codes were consumed before the dots arrived
             }
         }
         if (!alive) break;
-        if (shape.ablate & 4) continue;
-        // y: per row 16 pairs of adjacent columns, 8 columns apart
+        if (row >= shape.m) continue;
+        // y: this thread's row, 32 adjacent columns
+        float out[COLUMNS];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int row = m0 + fragment_row + 8 * i;
-            if (row >= shape.m) continue;
+        for (int j = 0; j < COLUMNS / 2; ++j) unpack_f32x2(acc[j], out[2 * j], out[2 * j + 1]);
+        if (bias != nullptr) {
 #pragma unroll
-            for (int j = 0; j < COLUMNS / 8; ++j) {
-                const int col = n0 + 8 * j + pair_column;
-                if (col >= shape.n) continue;
-                float lo = acc[i][2 * j], hi = acc[i][2 * j + 1];
-                if (bias != nullptr) {
-                    const float2 add = __ldg(reinterpret_cast<const float2 *>(bias + col));
-                    lo += add.x, hi += add.y;
-                }
-                if (shape.y_is_half)
-                    *reinterpret_cast<__half2 *>(static_cast<__half *>(y) + static_cast<size_t>(row) * shape.ldy + col) = __floats2half2_rn(lo, hi);
-                else
-                    *reinterpret_cast<float2 *>(static_cast<float *>(y) + static_cast<size_t>(row) * shape.ldy + col) = make_float2(lo, hi);
+            for (int j = 0; j < COLUMNS; ++j)
+                if (n0 + j < shape.n) out[j] += __ldg(bias + n0 + j);
+        }
+        const size_t element = static_cast<size_t>(row) * shape.ldy + n0;
+        // whole 32-byte sectors when the row segment is aligned for them, else element by element
+        const bool sectors = n0 + COLUMNS <= shape.n &&
+                             (reinterpret_cast<uintptr_t>(y) & 31) == 0 && shape.ldy % (shape.y_is_half ? 16 : 8) == 0;
+        if (shape.y_is_half) {
+            uint32_t packed[COLUMNS / 2];
+#pragma unroll
+            for (int j = 0; j < COLUMNS / 2; ++j) {
+                const __half2 h = __floats2half2_rn(out[2 * j], out[2 * j + 1]);
+                packed[j] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            __half *target = static_cast<__half *>(y) + element;
+            if (sectors) {
+#pragma unroll
+                for (int j = 0; j < COLUMNS / 16; ++j)
+                    st_global_v8(target + 16 * j, *reinterpret_cast<const uint32_t(*)[8]>(&packed[8 * j]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < COLUMNS; ++j)
+                    if (n0 + j < shape.n) target[j] = __float2half_rn(out[j]);
+            }
+        } else {
+            float *target = static_cast<float *>(y) + element;
+            if (sectors) {
+#pragma unroll
+                for (int j = 0; j < COLUMNS / 8; ++j)
+                    st_global_v8(target + 8 * j, *reinterpret_cast<const uint32_t(*)[8]>(&out[8 * j]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < COLUMNS; ++j)
+                    if (n0 + j < shape.n) target[j] = out[j];
             }
         }
     }
@@ -285,13 +334,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint8_t *tile_a = smem;
     uint8_t *tile_b = tile_a + STAGES * A_BYTES;
     float *sw_tile = reinterpret_cast<float *>(tile_b + STAGES * B_BYTES);
-    __half2 *sw_ring = reinterpret_cast<__half2 *>(reinterpret_cast<uint8_t *>(sw_tile) + STAGES * SCALE_BYTES);
-    uint64_t *full = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(sw_ring) + RING_BYTES);
+    float2 *sa_tile = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(sw_tile) + STAGES * SW_BYTES);
+    __half2 *ring = reinterpret_cast<__half2 *>(reinterpret_cast<uint8_t *>(sa_tile) + STAGES * SA_BYTES);
+    uint64_t *full = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(ring) + RING_BYTES);
     uint64_t *scale_ready = full + STAGES;
     uint64_t *empty = scale_ready + STAGES;
     uint64_t *dot_full = empty + STAGES;
-    uint64_t *dot_empty = dot_full + BUFFERS;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(dot_empty + BUFFERS);
+    uint64_t *dot_empty = dot_full + TEAMS * BUFFERS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(dot_empty + TEAMS * BUFFERS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = cluster_ctarank();  // 0 = leader
@@ -302,17 +352,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbarrier_init(&full[s], 1);                 // the leader's is the one in use
-            mbarrier_init(&scale_ready[s], SCALE_WARPS);
-            mbarrier_init(&empty[s], 1 + FOLD_WARPS);   // pair commit + this CTA's fold warps
+            mbarrier_init(&scale_ready[s], 1);
+            // This CTA's fold warps. They arrive after they have seen the dots of both groups of the
+            // stage, and a tcgen05.commit arrives only when the MMAs before it have read their operands:
+            // so the codes of the stage are free as well, in both CTAs, without a commit of their own.
+            mbarrier_init(&empty[s], FOLD_WARPS);
         }
-        for (int b = 0; b < BUFFERS; ++b) {
-            mbarrier_init(&dot_full[b], 1);             // pair commit
-            mbarrier_init(&dot_empty[b], 2 * FOLD_WARPS);  // the leader's: fold warps of both CTAs
+        for (int b = 0; b < TEAMS * BUFFERS; ++b) {
+            mbarrier_init(&dot_full[b], 1);                        // pair commit
+            mbarrier_init(&dot_empty[b], 2 * FOLD_WARPS / TEAMS);  // the leader's: the team's fold warps of both CTAs
         }
         fence_barrier_init();
     }
-    if (warp == MMA_WARP) {
-        tmem_alloc_pair(tmem_slot, BUFFERS * BN);
+    if (warp == MMA_WARP0) {
+        tmem_alloc_pair(tmem_slot, TEAMS * BUFFERS * TEAM_COLUMNS);
         tmem_relinquish_pair();
     }
     tcgen05_fence_before();
@@ -320,64 +373,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     cluster_sync();  // both CTAs' barriers exist before anything arrives on them from the other side
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const View view = {sw_tile, sw_ring, scale_ready, empty, dot_full, dot_empty, tmem_base, cta,
-                       pair, pairs, tiles, tiles_m, k_stages, groups};
+    const View view = {tile_a, tile_b, sw_tile, sa_tile, ring, full, scale_ready, empty, dot_full, dot_empty,
+                       tmem_base, cta, pair, pairs, tiles, tiles_m, k_stages, groups};
 
     if (warp < FOLD_WARP0) {
-      setmaxnreg_dec<CONTROL_REGISTERS>();
-      if (warp == PRODUCER_WARP) {
-        if (lane == 0) {
-            prefetch_tensormap(&map_a);
-            prefetch_tensormap(&map_w);
-            uint32_t iteration = 0;
-            bool alive = true;
-            for (int tile = pair; tile < tiles && alive; tile += pairs) {
-                const int m0 = (tile % tiles_m) * 2 * BM + cta * BM, n0 = (tile / tiles_m) * BN + cta * (BN / 2);
-                for (int ks = 0; ks < k_stages; ++ks, ++iteration) {
-                    const int s = iteration % STAGES;
-                    const uint32_t phase = (iteration / STAGES) & 1;
-                    if (!mbarrier_wait(&empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x5000 | s)) { alive = false; break; }
-                    // the leader expects the bytes of both CTAs' loads on its barrier
-                    if (cta == 0) mbarrier_arrive_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
-                    tma_load_2d_pair(tile_a + s * A_BYTES, &map_a, &full[s], ks * STAGE_K, m0);
-                    tma_load_2d_pair(tile_b + s * B_BYTES, &map_w, &full[s], ks * STAGE_K, n0);
-                }
-            }
+        setmaxnreg_dec<CONTROL_REGISTERS>();
+        if (warp == STAGING_WARP) {
+            staging_role(view, &map_a, &map_w, a_scales, w_scales, shape, lane);
+        } else if (lane == 0 && cta == 0 && warp >= MMA_WARP0 && warp < MMA_WARP0 + MMA_WARPS) {
+            mma_role(view, static_cast<uint32_t>(warp - MMA_WARP0));
         }
-      } else if (warp == MMA_WARP) {
-        if (lane == 0 && cta == 0) {
-            constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * BM, BN);
-            uint32_t iteration = 0, group_count = 0;
-            bool alive = true;
-            for (int tile = pair; tile < tiles && alive; tile += pairs) {
-                for (int ks = 0; ks < k_stages && alive; ++ks, ++iteration) {
-                    const int s = iteration % STAGES;
-                    const uint32_t phase = (iteration / STAGES) & 1;
-                    if (!mbarrier_wait(&full[s], phase, &g_status, STATUS_WAIT_FULL | 0x5000 | s)) { alive = false; break; }
-                    const uint32_t a_address = smem_u32(tile_a + s * A_BYTES);
-                    const uint32_t b_address = smem_u32(tile_b + s * B_BYTES);
-#pragma unroll
-                    for (int gl = 0; gl < 2; ++gl, ++group_count) {
-                        const uint32_t buffer = group_count % BUFFERS, buffer_phase = (group_count / BUFFERS) & 1;
-                        if (!mbarrier_wait(&dot_empty[buffer], buffer_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x5000 | buffer)) { alive = false; break; }
-                        tcgen05_fence_after();
-#pragma unroll
-                        for (int kk = 0; kk < 2; ++kk)
-                            if (!(shape.ablate & 16))
-                                umma_f8_pair(tmem_base + buffer * BN, umma_desc_k_sw128(a_address + gl * 64 + kk * 32),
-                                             umma_desc_k_sw128(b_address + gl * 64 + kk * 32), idesc, kk);
-                        tcgen05_commit_pair(&dot_full[buffer]);
-                    }
-                    if (alive) tcgen05_commit_pair(&empty[s]);
-                }
-            }
-        }
-      } else {
-        scale_role(view, w_scales, shape, static_cast<int>(threadIdx.x) - SCALE_WARP0 * 32, lane);
-      }
     } else {
         setmaxnreg_inc<FOLD_REGISTERS>();
-        fold_role<DUMP_DOTS>(view, a_scales, bias, y, dots_out, shape, warp, lane);
+        fold_role<DUMP_DOTS>(view, bias, y, dots_out, shape, warp, lane);
     }
 
     tcgen05_fence_before();
@@ -387,10 +395,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     __syncwarp();
     cluster_sync();  // neither CTA may leave while the other can still reach its shared memory or barriers
-    if (warp == MMA_WARP) {
+    if (warp == MMA_WARP0) {
         __syncwarp();
         tcgen05_fence_after();
-        tmem_dealloc_pair(tmem_base, BUFFERS * BN);
+        tmem_dealloc_pair(tmem_base, TEAMS * BUFFERS * TEAM_COLUMNS);
     }
 }
 

@@ -432,6 +432,31 @@ def test_w4a4_wide_gemm_bits_and_exact_dots(qi, wide_kernel, m, n, k):
     assert distance <= FP16_STORE_ULPS
 
 
+@pytest.mark.parametrize("m,n,k", [(2304, 2048, 1024), (1000, 1280, 3072), (4096, 3072, 640), (333, 4224, 2048),
+                                   (2048, 1152, 12288)])
+def test_w4a4_wide_gemm_equals_packed_kernel_on_many_tiles(qi, wide_kernel, m, n, k):
+    # Shapes with more tiles than CTA pairs, ragged row counts and long K: every CTA walks several tiles and the
+    # pipelines wrap many times. The byte-operand kernels must give the packed kernel's bits, launch after launch.
+    generator = torch.Generator(device="cuda").manual_seed(m + n + k)
+    def signed_codes(rows):
+        v = torch.randint(-7, 8, (rows, k), dtype=torch.int16, device="cuda", generator=generator) & 0xF
+        return (v[:, 0::2] | (v[:, 1::2] << 4)).to(torch.uint8).contiguous()
+    a_codes, w_codes = signed_codes(m), signed_codes(n)
+    a_scales = (torch.rand(m, k // 64, device="cuda", generator=generator) * 0.5 + 0.05).half()
+    w_scales = (torch.rand(n, k // 64, device="cuda", generator=generator) * 5e-3 + 1e-3).half()
+    a_wide, w_wide = (torch.zeros(r, k, dtype=torch.uint8, device="cuda") for r in (m, n))
+    assert qi.w4a4_widen_codes_ex(a_codes, a_wide, m, k) == 0
+    assert qi.w4a4_widen_codes_ex(w_codes, w_wide, n, k) == 0
+    expected = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    assert qi.w4a4_gemm_ex(a_codes, a_scales, w_codes, w_scales, None, expected, qi.DTYPE_F32, n, m, n, k) == 0
+    check_status(qi)
+    for _ in range(4):
+        y = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        assert qi.w4a4_gemm_wide_ex(a_wide, a_scales, w_wide, w_scales, None, y, qi.DTYPE_F32, n, m, n, k) == 0
+        check_status(qi)
+        assert torch.equal(y, expected)
+
+
 def test_w4a4_wide_gemm_extreme_dots(qi, wide_kernel):
     # all codes +-7: every group dot is +-3136, the largest the format allows; fp32 accumulation must stay exact
     m, n, k = 128, 128, 512
