@@ -43,6 +43,8 @@ METRIC = "packed W4A4/W4A16 GEMM TOPS at M=4096 block shapes, % of tensor/HBM ro
 UNIT = "TOPS"
 WORKLOAD = "qwen-image MMDiT block image stream, W4A4 H256 g64, M=4096 hidden=3072: qkv 3072->9216, out 3072->3072, fc1 3072->12288, fc2 12288->3072"
 CPU_SAMPLE_ROWS = 256
+# DRAM bytes of one w4a4_pair::gemm_kernel launch of average size (42.3 MB read + 36.9 MB written), from ncu
+NCU_TRAFFIC_BYTES_PER_AVERAGE_LAUNCH = 79.1e6
 
 
 def measured_peaks():
@@ -141,6 +143,83 @@ def make_activations(torch, generator, m, k, kind, device):
     elif kind == "gelu":
         x = torch.nn.functional.gelu(x, approximate="tanh")
     return x.half().contiguous()
+
+
+# ---- the path's other kernels, each against its own roofline ---------------------------------------
+
+def other_kernels(qi, torch, device, stream, peaks, m):
+    """W4A16 GEMM on the block's four shapes (tensor bound), the W4A16 M=1 GEMV and the activation
+    quantiser (HBM bound), timed with CUDA events around a CUDA graph on `stream`. GEMV weights rotate through more
+    copies than fit in L2; the other inputs are larger than L2 by themselves or compute bound."""
+    handle = stream.cuda_stream
+    generator = torch.Generator(device=device)
+    generator.manual_seed(4321)
+
+    def timed(launch, count):
+        """Average device time of `count` launches replayed from one CUDA graph: the kernels here run for
+        a few microseconds, less than the host needs to issue one launch through ctypes."""
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                assert launch(i) == 0, "a launch was refused"
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(count):
+                    launch(i)
+            graph.replay()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record(stream)
+            graph.replay()
+            end.record(stream)
+            torch.cuda.synchronize()
+        return begin.elapsed_time(end) / count
+
+    def affine_pack(n, k):
+        codes = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=device, generator=generator)
+        scales = (torch.rand(n, k // 64, device=device, generator=generator) * 0.006 + 0.002).half()
+        return codes, scales, (-8.0 * scales.float()).half()
+
+    out = {"w4a16_gemm": [], "peak_source": peaks["source"]}
+    flops = seconds = 0.0
+    for name, n, k, _ in LINEARS:
+        codes, scales, minimums = affine_pack(n, k)
+        x = torch.randn(m, k, device=device, generator=generator).half()
+        y = torch.empty(m, n, dtype=torch.float16, device=device)
+        ms = timed(lambda i: qi.w4a16_gemm_ex(x, codes, scales, minimums, None, y, qi.DTYPE_F16, n, m, n, k, handle), 20)
+        flops += 2.0 * m * n * k
+        seconds += ms * 1e-3
+        out["w4a16_gemm"].append({"linear": name, "ms": ms, "tflops": 2.0 * m * n * k / ms / 1e9})
+        del codes, scales, minimums, x, y
+    achieved = flops / seconds / 1e12
+    out["w4a16_gemm_roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
+                                  "frac": achieved / peaks["bf16_sustained"]}
+
+    n, k = 9216, 3072  # q/k/v of one token: the decode-shaped call
+    copies = [affine_pack(n, k) for _ in range(12)]  # 12 x 15.4 MB: no copy is still in L2 when its turn comes again
+    x1 = torch.randn(1, k, device=device, generator=generator).half()
+    y1 = torch.empty(1, n, dtype=torch.float16, device=device)
+    ms = timed(lambda i: qi.w4a16_gemv_ex(x1, *copies[i % 12], None, y1, qi.DTYPE_F16, n, 1, n, k, handle), 48)
+    gemv_bytes = n * k // 2 + 2 * n * (k // 64) * 2 + 2 * k + 2 * n
+    out["w4a16_gemv"] = {"n": n, "k": k, "us": ms * 1e3, "bytes": gemv_bytes,
+                         "roofline": {"bound": "hbm", "achieved": gemv_bytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                      "frac": gemv_bytes / ms / 1e6 / peaks["hbm_gbs"]}}
+    del copies
+
+    out["quantiser"] = []
+    for k in (3072, 12288):
+        sets = 8 if k == 3072 else 3  # rotating inputs: 8 x 25 MB or 3 x 101 MB
+        xs = [torch.randn(m, k, device=device, generator=generator).half() for _ in range(sets)]
+        scales = torch.empty(m, k // 64, dtype=torch.float16, device=device)
+        wide = torch.empty(m, k, dtype=torch.uint8, device=device)
+        ms = timed(lambda i: qi.w4a4_quantize_activations_wide_ex(xs[i % sets], qi.DTYPE_F16, None, scales, wide, m, k, handle), 4 * sets)
+        traffic = m * k * 2 + m * k + m * (k // 64) * 2
+        out["quantiser"].append({"k": k, "us": ms * 1e3, "bytes": traffic,
+                                 "roofline": {"bound": "hbm", "achieved": traffic / ms / 1e6, "peak": peaks["hbm_gbs"],
+                                              "unit": "GB/s", "frac": traffic / ms / 1e6 / peaks["hbm_gbs"]}})
+        del xs, scales, wide
+    assert qi.kernel_status() == 0, "a kernel gave up on a wait"
+    return out
 
 
 # ---- the b200 arm ---------------------------------------------------------------------------------
@@ -310,12 +389,17 @@ def run_b200(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "roofline": {"kernel": "w4a4::gemm_kernel" if args.w4a4_path == "packed" else "w4a4_pair::gemm_kernel", "bound": "tensor", "achieved": achieved, "peak": int8_peak,
-                         "unit": "TOP/s", "frac": achieved / int8_peak, "traffic": None,
+                         "unit": "TOP/s", "frac": achieved / int8_peak,
+                         "traffic": (NCU_TRAFFIC_BYTES_PER_AVERAGE_LAUNCH / world) if args.w4a4_path == "wide" else None,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the qkv launch "
+                                           "(its 2MNK is the average of the four launches), profiles/w4a4_pair_gemm_block_m4096.md",
                          "peak_source": f"2 x the sustained bf16 figure of MEASURED_PEAKS.json ({peaks['source']}); "
                                         "no 8-bit figure is measured; fp8 and int8 run at twice the bf16 rate",
                          "launches_timed": len(gemm_events), "avg_launch_ms": gemm_ms / max(1, len(gemm_events))},
             "clocks": sampler.summary(),
         }
+        if world == 1 and not args.no_other_kernels:
+            result["other_kernels"] = other_kernels(qi, torch, device, stream, peaks, m)
     if dist is not None:
         torch.cuda.synchronize()
         context.destroy()
@@ -326,9 +410,10 @@ def run_b200(args):
 
 # ---- the CPU arm: the oracle port on this host's cores ----------------------------------------------
 
-def cpu_port(rows: int, repeats: int, warmup: int):
+def cpu_port(rows: int, repeats: int, warmup: int, min_seconds: float = 0.0):
     """Times the CPU restatement of the same four linears (oracle/qipack_oracle.c, threaded over all
-    host cores) on the first `rows` activation rows. Returns (TOPS, cores, seconds per pass)."""
+    host cores) on the first `rows` activation rows, `repeats` passes or more until `min_seconds` have
+    gone by. Returns (TOPS, cores, seconds per pass)."""
     import numpy as np
     from oracle import qipack_oracle as qo
 
@@ -345,10 +430,12 @@ def cpu_port(rows: int, repeats: int, warmup: int):
         for x, codes, scales in work[:1]:
             qo.w4a4_linear_fast(x, codes, scales, threads=cores)
     start = time.perf_counter()
-    for _ in range(repeats):
+    passes = 0
+    while passes < repeats or time.perf_counter() - start < min_seconds:
         for x, codes, scales in work:
             qo.w4a4_linear_fast(x, codes, scales, threads=cores)
-    seconds = (time.perf_counter() - start) / repeats
+        passes += 1
+    seconds = (time.perf_counter() - start) / passes
     ops = sum(2.0 * rows * n * k for _, n, k, _ in LINEARS)
     return ops / seconds / 1e12, cores, seconds
 
@@ -360,7 +447,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
-    steps = max(1, min(args.steps, 3))
+    steps = max(1, min(args.steps, 60))  # a pass takes a few tenths of a second: the run stays well under a minute
     tops, cores, seconds = cpu_port(CPU_SAMPLE_ROWS, steps, min(args.warmup, 1))
     sample = f"first {CPU_SAMPLE_ROWS} of {M_TOKENS} rows of each of the four linears, activation quantisation included"
     return {
@@ -380,7 +467,9 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
-    parser.add_argument("--w4a4-path", default="packed", choices=["packed", "wide"],
+    parser.add_argument("--no-other-kernels", action="store_true",
+                        help="skip the W4A16 GEMM / GEMV / quantiser figures (profiling runs)")
+    parser.add_argument("--w4a4-path", default="wide", choices=["packed", "wide"],
                         help="packed: the drop-in kernels on nibble-packed codes (int8 tensor-core dots); "
                              "wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
     args = parser.parse_args()
@@ -395,11 +484,11 @@ def main():
     if result is None:
         return
     if not args.no_cpu_baseline and result["n_gpus"] == 1:
-        tops, cores, seconds = cpu_port(CPU_SAMPLE_ROWS, 1, 1)
+        tops, cores, seconds = cpu_port(CPU_SAMPLE_ROWS, 1, 1, min_seconds=12.0)
         result["cpu_baseline"] = {
             "value": tops, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"first {CPU_SAMPLE_ROWS} of {M_TOKENS} rows of each of the four linears "
-                      f"({seconds:.1f} s of CPU work), activation quantisation included"}
+                      f"({seconds:.2f} s per pass, passes repeated for 12 s of CPU work), activation quantisation included"}
     print(json.dumps(result), flush=True)
 
 

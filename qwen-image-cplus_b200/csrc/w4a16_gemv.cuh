@@ -19,6 +19,7 @@ namespace w4a16 {
 
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+constexpr int GEMV_AHEAD = 3;  // steps whose loads are in flight together
 
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -38,7 +39,7 @@ __device__ __forceinline__ uint32_t unpack_byte(uint32_t word, int byte, __half2
 }
 
 // k_splits * row_tiles == GEMV_WARPS. Block b owns weight rows [16 * row_tiles * b, ...).
-__global__ void __launch_bounds__(GEMV_THREADS)
+__global__ void __launch_bounds__(GEMV_THREADS, 2)
 gemv_kernel(const __half *__restrict__ x, const uint8_t *__restrict__ codes, const __half *__restrict__ scales,
             const __half *__restrict__ minimums, const float *__restrict__ bias, void *__restrict__ y,
             int m, int n, int k, long long ldy, int y_is_half, int k_splits) {
@@ -54,35 +55,53 @@ gemv_kernel(const __half *__restrict__ x, const uint8_t *__restrict__ codes, con
     float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (rows_inside) {
         const size_t row_a = static_cast<size_t>(n0 + r), row_b = row_a + 8;
-        for (int quad = k_split; quad < quads; quad += k_splits) {
-            // every lane runs the same mma.sync; a lane past a ragged last quad feeds zeros
-            const int g = quad * 4 + q;
-            const bool valid = g < groups;
-            const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-            const uint4 *pa = reinterpret_cast<const uint4 *>(codes + row_a * (k / 2) + g * 32);
-            const uint4 *pb = reinterpret_cast<const uint4 *>(codes + row_b * (k / 2) + g * 32);
-            const uint4 a_lo = valid ? __ldg(pa) : zero, a_hi = valid ? __ldg(pa + 1) : zero;
-            const uint4 b_lo = valid ? __ldg(pb) : zero, b_hi = valid ? __ldg(pb + 1) : zero;
-            const __half nothing = __ushort_as_half(0);
-            const __half2 sa = __half2half2(valid ? __ldg(scales + row_a * groups + g) : nothing);
-            const __half2 ma = __half2half2(valid ? __ldg(minimums + row_a * groups + g) : nothing);
-            const __half2 sb = __half2half2(valid ? __ldg(scales + row_b * groups + g) : nothing);
-            const __half2 mb = __half2half2(valid ? __ldg(minimums + row_b * groups + g) : nothing);
-            const uint32_t wa[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
-            const uint32_t wb[8] = {b_lo.x, b_lo.y, b_lo.z, b_lo.w, b_hi.x, b_hi.y, b_hi.z, b_hi.w};
-            // activation row (lane / 4) supplies the B operand for the same 64 inputs
-            const uint4 *px = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(r) * k + g * 64);
-            const bool has_x = valid && r < m;
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        const __half nothing = __ushort_as_half(0);
+        // Latency, not arithmetic, is what this kernel pays for: a warp has only a few steps, and a step
+        // that waits for its own loads costs a full trip to HBM. So the loads of up to GEMV_AHEAD steps
+        // (2 KB of codes per warp and step) are all issued before the first one is used.
+        for (int quad0 = k_split; quad0 < quads; quad0 += k_splits * GEMV_AHEAD) {
+            uint4 code_a[GEMV_AHEAD][2], code_b[GEMV_AHEAD][2];
+            __half scale_a[GEMV_AHEAD], minimum_a[GEMV_AHEAD], scale_b[GEMV_AHEAD], minimum_b[GEMV_AHEAD];
 #pragma unroll
-            for (int w = 0; w < 8; ++w) {  // 8 inputs (4 bytes of each row) per word, two MMA steps
-                const uint4 xv = has_x ? __ldg(px + w) : zero;
-                uint32_t a[4];
-                a[0] = unpack_byte(wa[w], 0, sa, ma), a[1] = unpack_byte(wb[w], 0, sb, mb);
-                a[2] = unpack_byte(wa[w], 1, sa, ma), a[3] = unpack_byte(wb[w], 1, sb, mb);
-                mma_m16n8k16(c, a, xv.x, xv.y);
-                a[0] = unpack_byte(wa[w], 2, sa, ma), a[1] = unpack_byte(wb[w], 2, sb, mb);
-                a[2] = unpack_byte(wa[w], 3, sa, ma), a[3] = unpack_byte(wb[w], 3, sb, mb);
-                mma_m16n8k16(c, a, xv.z, xv.w);
+            for (int i = 0; i < GEMV_AHEAD; ++i) {
+                // every lane runs the same mma.sync; a lane past a ragged end feeds zeros
+                const int g = (quad0 + i * k_splits) * 4 + q;
+                const bool valid = g < groups;
+                const uint4 *pa = reinterpret_cast<const uint4 *>(codes + row_a * (k / 2) + g * 32);
+                const uint4 *pb = reinterpret_cast<const uint4 *>(codes + row_b * (k / 2) + g * 32);
+                code_a[i][0] = valid ? __ldg(pa) : zero, code_a[i][1] = valid ? __ldg(pa + 1) : zero;
+                code_b[i][0] = valid ? __ldg(pb) : zero, code_b[i][1] = valid ? __ldg(pb + 1) : zero;
+                scale_a[i] = valid ? __ldg(scales + row_a * groups + g) : nothing;
+                minimum_a[i] = valid ? __ldg(minimums + row_a * groups + g) : nothing;
+                scale_b[i] = valid ? __ldg(scales + row_b * groups + g) : nothing;
+                minimum_b[i] = valid ? __ldg(minimums + row_b * groups + g) : nothing;
+            }
+#pragma unroll
+            for (int i = 0; i < GEMV_AHEAD; ++i) {
+                const int g = (quad0 + i * k_splits) * 4 + q;
+                if ((quad0 + i * k_splits) >= quads) break;  // uniform over the warp
+                const bool valid = g < groups;
+                const __half2 sa = __half2half2(scale_a[i]), ma = __half2half2(minimum_a[i]);
+                const __half2 sb = __half2half2(scale_b[i]), mb = __half2half2(minimum_b[i]);
+                const uint32_t wa[8] = {code_a[i][0].x, code_a[i][0].y, code_a[i][0].z, code_a[i][0].w,
+                                        code_a[i][1].x, code_a[i][1].y, code_a[i][1].z, code_a[i][1].w};
+                const uint32_t wb[8] = {code_b[i][0].x, code_b[i][0].y, code_b[i][0].z, code_b[i][0].w,
+                                        code_b[i][1].x, code_b[i][1].y, code_b[i][1].z, code_b[i][1].w};
+                // activation row (lane / 4) supplies the B operand for the same 64 inputs
+                const uint4 *px = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(r) * k + g * 64);
+                const bool has_x = valid && r < m;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {  // 8 inputs (4 bytes of each row) per word, two MMA steps
+                    const uint4 xv = has_x ? __ldg(px + w) : zero;
+                    uint32_t a[4];
+                    a[0] = unpack_byte(wa[w], 0, sa, ma), a[1] = unpack_byte(wb[w], 0, sb, mb);
+                    a[2] = unpack_byte(wa[w], 1, sa, ma), a[3] = unpack_byte(wb[w], 1, sb, mb);
+                    mma_m16n8k16(c, a, xv.x, xv.y);
+                    a[0] = unpack_byte(wa[w], 2, sa, ma), a[1] = unpack_byte(wb[w], 2, sb, mb);
+                    a[2] = unpack_byte(wa[w], 3, sa, ma), a[3] = unpack_byte(wb[w], 3, sb, mb);
+                    mma_m16n8k16(c, a, xv.z, xv.w);
+                }
             }
         }
     }
