@@ -14,7 +14,8 @@ sharded by output columns, rank r computes y[:, r*N/R:(r+1)*N/R] and the slices 
 all-gathered over NVLink; total work is fixed (strong scaling).
 
 Prints ONE JSON line. `value` is device-timed with inputs resident in HBM; `e2e` is the same
-metric through the C ABI with host buffers (pinned) copied in and results copied out every step;
+metric through the C ABI with host buffers (pinned) copied in and results copied out every step
+(copies of neighbouring steps overlap the kernels on separate streams);
 `roofline` is the W4A4 GEMM kernel's achieved rate from CUDA events around its launches inside
 the timed region; `cpu_baseline` is the CPU oracle port timed on this host on a bounded sample.
 """
@@ -276,14 +277,17 @@ def run_b200(args):
 
     launches = {"count": 0}
 
-    def step(record_gemm_events=None):
+    def step(record_gemm_events=None, slot=None):
+        """One pass over the four linears. `slot` selects the end-to-end path's own input/output buffers."""
         for layer in layers:
             k, n_local = layer["k"], layer["n_local"]
+            x_in = layer["x"] if slot is None else layer["x_slots"][slot]
+            y_out = layer["y_local"] if slot is None else layer["y_slots"][slot]
             if args.w4a4_path == "wide":
-                status = qi.w4a4_quantize_activations_wide_ex(layer["x"], qi.DTYPE_F16, None, layer["a_scales"],
+                status = qi.w4a4_quantize_activations_wide_ex(x_in, qi.DTYPE_F16, None, layer["a_scales"],
                                                               layer["a_wide"], m, k, stream_handle)
             else:
-                status = qi.w4a4_quantize_activations_ex(layer["x"], qi.DTYPE_F16, layer["a_codes"], layer["a_scales"],
+                status = qi.w4a4_quantize_activations_ex(x_in, qi.DTYPE_F16, layer["a_codes"], layer["a_scales"],
                                                          m, k, stream_handle)
             assert status == 0, f"quantise {layer['name']}: cuda status {status}"
             if record_gemm_events is not None:
@@ -291,10 +295,10 @@ def run_b200(args):
                 start.record(stream)
             if args.w4a4_path == "wide":
                 status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
-                                              None, layer["y_local"], qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
+                                              None, y_out, qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
             else:
                 status = qi.w4a4_gemm_ex(layer["a_codes"], layer["a_scales"], layer["w_codes"], layer["w_scales"], None,
-                                         layer["y_local"], qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
+                                         y_out, qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
             assert status == 0, f"gemm {layer['name']}: cuda status {status}"
             if record_gemm_events is not None:
                 stop = torch.cuda.Event(enable_timing=True)
@@ -302,7 +306,7 @@ def run_b200(args):
                 record_gemm_events.append((start, stop, layer))
             launches["count"] += 2
             if context is not None:
-                status = context.all_gather(layer["y_local"], layer["y_all"], qi.DTYPE_F16, m, n_local, stream_handle)
+                status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, stream_handle)
                 assert status == 0, f"all-gather {layer['name']}: status {status}"
 
     def barrier():
@@ -334,29 +338,52 @@ def run_b200(args):
     gemm_ops = sum(2.0 * m * layer["n_local"] * layer["k"] for _, _, layer in gemm_events)
 
     # ---- end to end: host buffers in, host buffers out, every step
+    # Three streams and two sets of device buffers: while step s computes, the inputs of step s + 1 come in and the
+    # results of step s - 1 go out (PCIe is full duplex; the copies, not the kernels, set the pace).
     host_x = [layer["x"].cpu().pin_memory() for layer in layers]
     host_y = [torch.empty(m, layer["n_local"], dtype=torch.float16).pin_memory() for layer in layers]
     h2d = sum(t.numel() * t.element_size() for t in host_x)
     d2h = sum(t.numel() * t.element_size() for t in host_y)
+    for layer in layers:
+        layer["x_slots"] = [torch.empty_like(layer["x"]) for _ in range(2)]
+        layer["y_slots"] = [torch.empty_like(layer["y_local"]) for _ in range(2)]
+    in_stream, out_stream = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+    computed = [None, None]   # event: the kernels that read x_slots[i] / wrote y_slots[i] are done
+    copied_out = [None, None]  # event: y_slots[i] has reached the host
 
-    def e2e_step():
-        with torch.cuda.stream(stream):
+    def e2e_step(index):
+        slot = index % 2
+        if computed[slot] is not None:
+            in_stream.wait_event(computed[slot])       # the step that read this input slot is done
+        with torch.cuda.stream(in_stream):
             for layer, hx in zip(layers, host_x):
-                layer["x"].copy_(hx, non_blocking=True)
-        step()
-        with torch.cuda.stream(stream):
+                layer["x_slots"][slot].copy_(hx, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record(in_stream)
+        stream.wait_event(arrived)
+        if copied_out[slot] is not None:
+            stream.wait_event(copied_out[slot])         # the results last written to this output slot are on the host
+        step(slot=slot)
+        computed[slot] = torch.cuda.Event()
+        computed[slot].record(stream)
+        out_stream.wait_event(computed[slot])
+        with torch.cuda.stream(out_stream):
             for layer, hy in zip(layers, host_y):
-                hy.copy_(layer["y_local"], non_blocking=True)
+                hy.copy_(layer["y_slots"][slot], non_blocking=True)
+        copied_out[slot] = torch.cuda.Event()
+        copied_out[slot].record(out_stream)
 
-    e2e_steps = max(2, min(args.steps, 10))
-    for _ in range(2):
-        e2e_step()
+    e2e_steps = max(4, min(args.steps, 20))
+    for index in range(4):
+        e2e_step(index)
     barrier()
     e2e_begin, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_begin.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_end.record(stream)
+    e2e_begin.record(in_stream)  # the streams are idle here: the first thing to run is the first copy on in_stream
+    for index in range(e2e_steps):
+        e2e_step(index)
+    out_stream.wait_stream(stream)
+    out_stream.wait_stream(in_stream)
+    e2e_end.record(out_stream)   # after the last result has reached the host
     barrier()
     e2e_ms = e2e_begin.elapsed_time(e2e_end)
 
