@@ -270,13 +270,17 @@ int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const 
     const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
     int tile = g_w4a16_tile;
     if (tile == 0) {
-        // Measured on B200 (4096 x {3072, 9216, 12288} x {3072, 12288}, 1024 and 256 rows):
-        // 256x256 on one CTA wins when there are at least two full waves of such tiles; the same
-        // tile on a CTA pair (half the unpacking per CTA, overlapped epilogue, 74 tiles per wave)
-        // wins below that; 128x128 wins when even pairs would leave most of the machine idle.
+        // Measured on B200 (4096 x {3072, 9216, 12288} x {3072, 12288}, 1024 and 256 rows): per tile the
+        // 256x256 tile on one CTA is about 4 % faster than the same tile on a CTA pair, but a pair wave is
+        // 74 tiles instead of 148, which wastes less of the last wave; below two single-CTA waves the pair
+        // (half the unpacking per CTA, overlapped epilogue) wins outright; 128x128 wins when even pairs
+        // would leave most of the machine idle.
         const int sms = sm_count(device);
         const long long tiles_256 = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
-        if (tiles_256 >= 2LL * sms) tile = 4;
+        const long long pairs = sms / 2;
+        const double single_waves = static_cast<double>((tiles_256 + sms - 1) / sms) / 1.04;
+        const double pair_waves = static_cast<double>((tiles_256 + pairs - 1) / pairs) / 2.0;
+        if (tiles_256 >= 2LL * sms) tile = single_waves <= pair_waves ? 4 : 5;
         else if (tiles_256 * 4 >= sms) tile = 5;
         else tile = 1;
     }

@@ -24,7 +24,7 @@ using w4a16::unpack32;
 constexpr int THREADS = 512;
 constexpr int BK = 64;
 constexpr int BM = 128, BN = 256;  // per CTA rows; pair tile is 256 x 256, each CTA unpacks 128 weight rows
-constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, EPILOGUE_WARP0 = 4, UNPACK_WARP0 = 8, UNPACK_WARPS = 8;
+constexpr int PRODUCER_WARP = 0, MMA_WARP = 1, MMA_WARPS = 2, EPILOGUE_WARP0 = 4, UNPACK_WARP0 = 8, UNPACK_WARPS = 8;
 constexpr int ACC_STAGES = 2;
 constexpr int A_BYTES = BM * 128, B_BYTES = (BN / 2) * 128, C_BYTES = (BN / 2) * 32;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + C_BYTES;
@@ -34,7 +34,7 @@ template <int STAGES>
 struct Tile {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BARRIER_BYTES + 1024;
     static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
-    static_assert((4 * STAGES + 2 * ACC_STAGES) * 8 + 8 <= BARRIER_BYTES, "barrier block");
+    static_assert((4 * STAGES + 2 * ACC_STAGES + MMA_WARPS) * 8 + 8 <= BARRIER_BYTES, "barrier block");
 };
 
 template <int STAGES>
@@ -53,7 +53,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     uint64_t *empty = ready + STAGES;
     uint64_t *tmem_full = empty + STAGES;
     uint64_t *tmem_empty = tmem_full + ACC_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + ACC_STAGES);
+    uint64_t *token = tmem_empty + ACC_STAGES;  // passes the turn between the two MMA-issuing threads
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(token + MMA_WARPS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = cluster_ctarank();  // 0 = leader
@@ -69,9 +70,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
             mbarrier_init(&empty[s], 1);
         }
         for (int a = 0; a < ACC_STAGES; ++a) {
-            mbarrier_init(&tmem_full[a], 1);
+            mbarrier_init(&tmem_full[a], k_blocks < MMA_WARPS ? k_blocks : MMA_WARPS);  // one commit per issuing thread
             mbarrier_init(&tmem_empty[a], 2 * 4);
         }
+        for (int t = 0; t < MMA_WARPS; ++t) mbarrier_init(&token[t], 1);
         fence_barrier_init();
     }
     if (warp == MMA_WARP) {
@@ -104,31 +106,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 }
             }
         }
-    } else if (warp == MMA_WARP) {
+    } else if (warp >= MMA_WARP && warp < MMA_WARP + MMA_WARPS) {
+        // Two threads in two warps of the leader issue the MMAs, K block by K block in turn. A tcgen05.commit
+        // holds up the later tcgen05 instructions of the thread that issued it for about 440 cycles, as long
+        // as the 512 tensor cycles of a K block here: one thread alone leaves bubbles, and the other thread's
+        // instructions are not held up. A token passed between the two keeps the MMAs in K order, so the
+        // accumulation order - and every bit of y - is fixed.
         if (lane == 0 && cta == 0) {
             constexpr uint32_t idesc = umma_idesc_f16_f32(2 * BM, BN);
-            uint32_t iteration = 0, tile_count = 0;
-            bool alive = true;
-            for (int tile = pair; tile < tiles && alive; tile += pairs, ++tile_count) {
-                const uint32_t acc = tile_count % ACC_STAGES, acc_phase = (tile_count / ACC_STAGES) & 1;
-                if (!mbarrier_wait(&tmem_empty[acc], acc_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x7000 | acc)) break;
-                tcgen05_fence_after();
-                const uint32_t tmem_acc = tmem_base + acc * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++iteration) {
-                    const int s = iteration % STAGES;
-                    const uint32_t phase = (iteration / STAGES) & 1;
-                    if (!mbarrier_wait(&a_full[s], phase, &g_status, STATUS_WAIT_FULL | 0x7000 | s) ||
-                        !mbarrier_wait(&ready[s], phase, &g_status, STATUS_WAIT_READY | 0x7000 | s)) { alive = false; break; }
-                    tcgen05_fence_after();
-                    const uint32_t a_address = smem_u32(smem_a + s * A_BYTES);
-                    const uint32_t b_address = smem_u32(smem_b + s * B_BYTES);
-#pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)
-                        umma_f16_pair(tmem_acc, umma_desc_k_sw128(a_address + kk * 32), umma_desc_k_sw128(b_address + kk * 32),
-                                      idesc, (kb | kk) != 0 ? 1u : 0u);
-                    tcgen05_commit_pair(&empty[s]);
+            const uint32_t mine = warp - MMA_WARP;
+            uint32_t iteration = mine, tile_count = 0;
+            int kb = mine, tile = pair;
+            while (true) {
+                while (kb >= k_blocks) {
+                    kb -= k_blocks;
+                    tile += pairs;
+                    ++tile_count;
                 }
-                if (alive) tcgen05_commit_pair(&tmem_full[acc]);
+                if (tile >= tiles) break;
+                const uint32_t acc = tile_count % ACC_STAGES, acc_phase = (tile_count / ACC_STAGES) & 1;
+                const uint32_t tmem_acc = tmem_base + acc * BN;
+                const int s = iteration % STAGES;
+                const uint32_t phase = (iteration / STAGES) & 1;
+                if (!mbarrier_wait(&a_full[s], phase, &g_status, STATUS_WAIT_FULL | 0x7000 | s) ||
+                    !mbarrier_wait(&ready[s], phase, &g_status, STATUS_WAIT_READY | 0x7000 | s))
+                    break;
+                // the other thread has issued K block `iteration - 1` (thread 0 starts with the token)
+                const uint32_t round = (iteration / MMA_WARPS) & 1;
+                if (!mbarrier_wait(&token[mine], mine == 0 ? round ^ 1 : round, &g_status, STATUS_WAIT_READY | 0x7200 | mine)) break;
+                if (kb == 0 && !mbarrier_wait(&tmem_empty[acc], acc_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x7000 | acc)) break;
+                tcgen05_fence_after();
+                const uint32_t a_address = smem_u32(smem_a + s * A_BYTES);
+                const uint32_t b_address = smem_u32(smem_b + s * B_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)
+                    umma_f16_pair(tmem_acc, umma_desc_k_sw128(a_address + kk * 32), umma_desc_k_sw128(b_address + kk * 32),
+                                  idesc, (kb | kk) != 0 ? 1u : 0u);
+                mbarrier_arrive(&token[mine ^ 1]);
+                tcgen05_commit_pair(&empty[s]);
+                // the last K block of each thread closes the tile: together the commits cover every MMA of the tile
+                if (kb + MMA_WARPS >= k_blocks) tcgen05_commit_pair(&tmem_full[acc]);
+                iteration += MMA_WARPS;
+                kb += MMA_WARPS;
             }
         }
     } else if (warp >= UNPACK_WARP0) {
