@@ -276,6 +276,7 @@ def run_b200(args):
     torch.cuda.synchronize()
 
     launches = {"count": 0}
+    gather_stream = torch.cuda.Stream(device=device) if context is not None else None
 
     def step(record_gemm_events=None, slot=None):
         """One pass over the four linears. `slot` selects the end-to-end path's own input/output buffers."""
@@ -290,6 +291,8 @@ def run_b200(args):
                 status = qi.w4a4_quantize_activations_ex(x_in, qi.DTYPE_F16, layer["a_codes"], layer["a_scales"],
                                                          m, k, stream_handle)
             assert status == 0, f"quantise {layer['name']}: cuda status {status}"
+            if layer.get("gathered") is not None:
+                stream.wait_event(layer["gathered"])  # the previous gather of this linear has read its slice
             if record_gemm_events is not None:
                 start = torch.cuda.Event(enable_timing=True)
                 start.record(stream)
@@ -306,8 +309,16 @@ def run_b200(args):
                 record_gemm_events.append((start, stop, layer))
             launches["count"] += 2
             if context is not None:
-                status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, stream_handle)
+                # the gather of this linear runs on its own stream, under the next linear's kernels
+                computed_event = torch.cuda.Event()
+                computed_event.record(stream)
+                gather_stream.wait_event(computed_event)
+                status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, gather_stream.cuda_stream)
                 assert status == 0, f"all-gather {layer['name']}: status {status}"
+                layer["gathered"] = torch.cuda.Event()
+                layer["gathered"].record(gather_stream)
+        if context is not None:
+            stream.wait_stream(gather_stream)  # a step ends when its last slice has arrived everywhere
 
     def barrier():
         torch.cuda.synchronize()
