@@ -25,16 +25,17 @@
 //     loop with a lane-0 / shuffle wrapper around it cost 230, several times per group.
 //   * Integer division costs a warp over a hundred cycles: the per-stage roles walk the
 //     (tile, stage) sequence incrementally. Scales reach the fold threads as fp32 in shared memory,
-//     staged by one warp with cp.async several stages ahead; that warp also issues the TMA.
+//     staged by two warps with cp.async several stages ahead. The TMA has a thread of its own: when
+//     it shared a warp with the scale staging, the MMA threads waited for `full` most of the time.
 //   * A thread owns one output row: it stores whole 32-byte sectors (st.global.v8).
 //
 // Per CTA (rank 0 = leader issues the MMAs for both), 24 warps:
-//   warp 0      stage the scales (sa: this CTA's 128 rows, sw: the tile's 128 columns, two groups
-//               per stage) and issue the TMA for own A rows and own B rows
+//   warp 0      one thread: TMA for own A rows and own B rows
+//   warps 1, 2  stage the scales (sw: the tile's 128 columns; sa: this CTA's 128 rows; two groups per stage)
 //   warps 4-7   leader only, one thread each: tcgen05.mma.cta_group::2 kind::f8f6f4 (two K = 32 steps
 //               per group) and the commit that arrives on both CTAs' barriers
 //   warps 8-23  fold this CTA's 128 rows x 128 columns, 32 rows x 32 columns per warp
-//   (warps 1-3 only give up their registers: setmaxnreg works on groups of four warps)
+//   (warp 3 only gives up its registers: setmaxnreg works on groups of four warps)
 #pragma once
 #include "ptx.cuh"
 #include "w4a16_gemm.cuh"
@@ -51,7 +52,7 @@ constexpr int TEAM_COLUMNS = BN / TEAMS;
 constexpr int BUFFERS = 4;     // TMEM buffers of TEAM_COLUMNS fp32 columns per team
 constexpr int STAGES = 8;
 constexpr int TURNS = 2;       // MMA-issuing threads per team, taking turns group by group
-constexpr int STAGING_WARP = 0, MMA_WARP0 = 4, MMA_WARPS = TURNS * TEAMS, FOLD_WARP0 = 8, FOLD_WARPS = 16;  // warps 1-3 idle
+constexpr int PRODUCER_WARP = 0, SW_WARP = 1, SA_WARP = 2, MMA_WARP0 = 4, MMA_WARPS = TURNS * TEAMS, FOLD_WARP0 = 8, FOLD_WARPS = 16;  // warp 3 idle
 static_assert(MMA_WARP0 + MMA_WARPS <= FOLD_WARP0, "the issuing threads sit in control warps");
 constexpr int COLUMNS = BN / (FOLD_WARPS / 4);  // columns per fold warp: 32
 // Registers live in the four schedulers' own files (16384 each), and warp w runs on scheduler w % 4:
@@ -109,31 +110,46 @@ struct StageWalk {
     }
 };
 
-// Warp 0. Per stage: fetch the two groups' scales (one half2 per column and per row) SCALE_AHEAD
-// stages early with 4-byte cp.async; when the stage's buffers are free again, lane 0 starts the TMA
-// of this CTA's A rows and B rows and the warp writes the scales out as fp32: sw[group][column]
-// and sa[row] = (group 0, group 1).
-__device__ __forceinline__ void staging_role(const View &v, const CUtensorMap *map_a, const CUtensorMap *map_w,
-                                             const __half *__restrict__ a_scales, const __half *__restrict__ w_scales,
-                                             const GemmShape &shape, int lane) {
-    if (lane == 0) {
-        prefetch_tensormap(map_a);
-        prefetch_tensormap(map_w);
+// Warp 0, one thread: TMA of this CTA's A rows and of its half of each team's B rows, stage by stage.
+// It does nothing else: a clock trace showed the MMA threads waiting 700 cycles per stage for `full`
+// when the thread that issues the TMA also staged the scales (about 1450 cycles of serial work per stage).
+__device__ __forceinline__ void producer_role(const View &v, const CUtensorMap *map_a, const CUtensorMap *map_w) {
+    prefetch_tensormap(map_a);
+    prefetch_tensormap(map_w);
+    uint32_t s = 0, phase = 0;
+    for (StageWalk walk(v); !walk.done(v); walk.next(v)) {
+        if (!mbarrier_wait(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x5000 | s)) break;
+        const int m0 = walk.m_index * 2 * BM + static_cast<int>(v.cta) * BM;
+        const int n0 = walk.n_index * BN + static_cast<int>(v.cta) * B_BOX_ROWS;
+        // the leader expects the bytes of both CTAs' loads on its barrier
+        if (v.cta == 0) mbarrier_arrive_expect_tx(&v.full[s], 2 * (A_BYTES + B_BYTES));
+        tma_load_2d_pair(v.tile_a + s * A_BYTES, map_a, &v.full[s], walk.ks * STAGE_K, m0);
+#pragma unroll
+        for (int team = 0; team < TEAMS; ++team)  // this CTA's half of each team's columns
+            tma_load_2d_pair(v.tile_b + s * B_BYTES + team * (B_BOX_ROWS * 128), map_w, &v.full[s], walk.ks * STAGE_K,
+                             n0 + team * TEAM_COLUMNS);
+        if (++s == STAGES) s = 0, phase ^= 1;
     }
+}
+
+// Warps 1 and 2. Warp 1 stages the weight scales of the tile's 128 columns, warp 2 the activation scales of
+// this CTA's 128 rows: per stage the two groups' values (one half2 per column or row) are fetched
+// SCALE_AHEAD stages early with 4-byte cp.async and, when the stage is free again, written out as
+// fp32: sw[group][column] and sa[row] = (group 0, group 1).
+template <bool ROWS>
+__device__ __forceinline__ void scale_role(const View &v, const __half *__restrict__ values, int limit, int lane) {
+    constexpr int RING_OFFSET = ROWS ? BN : 0;
     StageWalk ahead(v);
     uint32_t ahead_slot = 0;
     auto fetch = [&]() {
         if (!ahead.done(v)) {
-            const int n0 = ahead.n_index * BN, m0 = ahead.m_index * 2 * BM + static_cast<int>(v.cta) * BM;
-            __half2 *slot = v.ring + ahead_slot * (BN + BM) + lane;
-            const __half *w_source = w_scales + static_cast<size_t>(n0 + lane) * v.groups + 2 * ahead.ks;
-            const __half *a_source = a_scales + static_cast<size_t>(m0 + lane) * v.groups + 2 * ahead.ks;
+            const int first = ROWS ? ahead.m_index * 2 * BM + static_cast<int>(v.cta) * BM : ahead.n_index * BN;
+            __half2 *slot = v.ring + ahead_slot * (BN + BM) + RING_OFFSET + lane;
+            const __half *source = values + static_cast<size_t>(first + lane) * v.groups + 2 * ahead.ks;
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                if (n0 + p * 32 + lane < shape.n) cp_async_4(slot + p * 32, w_source + static_cast<size_t>(p * 32) * v.groups);
+                if (first + p * 32 + lane < limit) cp_async_4(slot + p * 32, source + static_cast<size_t>(p * 32) * v.groups);
                 else slot[p * 32] = __halves2half2(__ushort_as_half(0), __ushort_as_half(0));
-                if (m0 + p * 32 + lane < shape.m) cp_async_4(slot + BN + p * 32, a_source + static_cast<size_t>(p * 32) * v.groups);
-                else slot[BN + p * 32] = __halves2half2(__ushort_as_half(0), __ushort_as_half(0));
             }
             ahead.next(v);
         }
@@ -145,32 +161,22 @@ __device__ __forceinline__ void staging_role(const View &v, const CUtensorMap *m
     for (StageWalk walk(v); !walk.done(v); walk.next(v)) {
         fetch();
         cp_async_wait<SCALE_AHEAD>();  // this thread's copies for this stage have landed
-        const __half2 *slot = v.ring + slot_index * (BN + BM) + lane;
-        float2 sw[4], sa[4];
+        const __half2 *slot = v.ring + slot_index * (BN + BM) + RING_OFFSET + lane;
+        float2 pair[4];
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            sw[p] = __half22float2(slot[p * 32]);
-            sa[p] = __half22float2(slot[BN + p * 32]);
-        }
+        for (int p = 0; p < 4; ++p) pair[p] = __half22float2(slot[p * 32]);
         if (!mbarrier_wait_warp(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x6000 | s, lane)) break;
-        if (lane == 0) {
-            const int m0 = walk.m_index * 2 * BM + static_cast<int>(v.cta) * BM;
-            const int n0 = walk.n_index * BN + static_cast<int>(v.cta) * B_BOX_ROWS;
-            // the leader expects the bytes of both CTAs' loads on its barrier
-            if (v.cta == 0) mbarrier_arrive_expect_tx(&v.full[s], 2 * (A_BYTES + B_BYTES));
-            tma_load_2d_pair(v.tile_a + s * A_BYTES, map_a, &v.full[s], walk.ks * STAGE_K, m0);
+        if (ROWS) {
+            float2 *sa_stage = v.sa_tile + s * BM + lane;
 #pragma unroll
-            for (int team = 0; team < TEAMS; ++team)  // this CTA's half of each team's columns
-                tma_load_2d_pair(v.tile_b + s * B_BYTES + team * (B_BOX_ROWS * 128), map_w, &v.full[s], walk.ks * STAGE_K,
-                                 n0 + team * TEAM_COLUMNS);
-        }
-        float *sw_stage = v.sw_tile + s * 2 * BN + lane;
-        float2 *sa_stage = v.sa_tile + s * BM + lane;
+            for (int p = 0; p < 4; ++p) sa_stage[p * 32] = pair[p];
+        } else {
+            float *sw_stage = v.sw_tile + s * 2 * BN + lane;
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            sw_stage[p * 32] = sw[p].x;
-            sw_stage[BN + p * 32] = sw[p].y;
-            sa_stage[p * 32] = sa[p];
+            for (int p = 0; p < 4; ++p) {
+                sw_stage[p * 32] = pair[p].x;
+                sw_stage[BN + p * 32] = pair[p].y;
+            }
         }
         __syncwarp();
         if (lane == 0) mbarrier_arrive(&v.scale_ready[s]);
@@ -352,7 +358,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbarrier_init(&full[s], 1);                 // the leader's is the one in use
-            mbarrier_init(&scale_ready[s], 1);
+            mbarrier_init(&scale_ready[s], 2);          // the two scale-staging warps
             // This CTA's fold warps. They arrive after they have seen the dots of both groups of the
             // stage, and a tcgen05.commit arrives only when the MMAs before it have read their operands:
             // so the codes of the stage are free as well, in both CTAs, without a commit of their own.
@@ -378,8 +384,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
     if (warp < FOLD_WARP0) {
         setmaxnreg_dec<CONTROL_REGISTERS>();
-        if (warp == STAGING_WARP) {
-            staging_role(view, &map_a, &map_w, a_scales, w_scales, shape, lane);
+        if (warp == PRODUCER_WARP) {
+            if (lane == 0) producer_role(view, &map_a, &map_w);
+        } else if (warp == SW_WARP) {
+            scale_role<false>(view, w_scales, shape.n, lane);
+        } else if (warp == SA_WARP) {
+            scale_role<true>(view, a_scales, shape.m, lane);
         } else if (lane == 0 && cta == 0 && warp >= MMA_WARP0 && warp < MMA_WARP0 + MMA_WARPS) {
             mma_role(view, static_cast<uint32_t>(warp - MMA_WARP0));
         }
