@@ -66,6 +66,9 @@ static_assert(THREADS % 128 == 0 && FOLD_WARP0 % 4 == 0, "setmaxnreg is a warpgr
 static_assert(THREADS / 128 * LAUNCH_REGISTERS * 32 <= 16384, "registers of one scheduler at launch");
 static_assert(FOLD_WARP0 / 4 * CONTROL_REGISTERS + FOLD_WARPS / 4 * FOLD_REGISTERS <= THREADS / 128 * LAUNCH_REGISTERS,
               "setmaxnreg.inc would wait for registers that do not exist");
+// Pause between polls of the roles that run stages ahead and therefore wait most of the time: a warp that spins
+// takes issue slots from the fold warps of its scheduler.
+constexpr uint32_t AHEAD_BACKOFF_NS = 256;
 constexpr int SCALE_AHEAD = 6, SCALE_RING = 8;  // stages of scales in flight; ring slots
 
 constexpr int A_BYTES = BM * 128, B_BYTES = (BN / 2) * 128;
@@ -118,7 +121,7 @@ __device__ __forceinline__ void producer_role(const View &v, const CUtensorMap *
     prefetch_tensormap(map_w);
     uint32_t s = 0, phase = 0;
     for (StageWalk walk(v); !walk.done(v); walk.next(v)) {
-        if (!mbarrier_wait(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x5000 | s)) break;
+        if (!mbarrier_wait(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x5000 | s, AHEAD_BACKOFF_NS)) break;
         const int m0 = walk.m_index * 2 * BM + static_cast<int>(v.cta) * BM;
         const int n0 = walk.n_index * BN + static_cast<int>(v.cta) * B_BOX_ROWS;
         // the leader expects the bytes of both CTAs' loads on its barrier
@@ -165,7 +168,7 @@ __device__ __forceinline__ void scale_role(const View &v, const __half *__restri
         float2 pair[4];
 #pragma unroll
         for (int p = 0; p < 4; ++p) pair[p] = __half22float2(slot[p * 32]);
-        if (!mbarrier_wait_warp(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x6000 | s, lane)) break;
+        if (!mbarrier_wait_warp(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x6000 | s, lane, AHEAD_BACKOFF_NS)) break;
         if (ROWS) {
             float2 *sa_stage = v.sa_tile + s * BM + lane;
 #pragma unroll
