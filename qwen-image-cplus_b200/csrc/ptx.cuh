@@ -313,10 +313,14 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
     return d;
 }
 
-// ---- cp.async (4-byte, global -> shared, per thread) --------------------------------------------
+// ---- cp.async (4- or 8-byte, global -> shared, per thread) --------------------------------------------
 
 __device__ __forceinline__ void cp_async_4(void *smem, const void *global) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem)), "l"(global) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_8(void *smem, const void *global) {  // both addresses 8-byte aligned
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem)), "l"(global) : "memory");
 }
 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }

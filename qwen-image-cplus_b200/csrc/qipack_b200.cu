@@ -196,10 +196,10 @@ int launch_w4a4_pair(const void *a_bytes, const void *a_scales, const void *w_by
     namespace wp = w4a4_pair;
     CUtensorMap map_a, map_w;
     if (!make_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_bytes, shape.k, shape.m, static_cast<uint64_t>(shape.k),
-                  wp::STAGE_K, wp::BM, CU_TENSOR_MAP_SWIZZLE_128B))
+                  128, wp::BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return INVALID;
     if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_bytes, shape.k, shape.n, static_cast<uint64_t>(shape.k),
-                  wp::STAGE_K, wp::B_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B))
+                  128, wp::B_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B))
         return INVALID;
     auto kernel = dots != nullptr ? wp::gemm_kernel<true> : wp::gemm_kernel<false>;
     static bool configured[MAX_DEVICES][2];
@@ -318,7 +318,7 @@ int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_byte
     const int device = current_device();
     if (device < 0) return INVALID;
     const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
-    if (g_w4a4_wide_single)
+    if (g_w4a4_wide_single || k % w4a4_pair::STAGE_K != 0)  // the pair kernel's stage is four groups
         return launch_w4a4_wide<6>(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
     return launch_w4a4_pair(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
 }

@@ -28,10 +28,12 @@
 //     staged by two warps with cp.async several stages ahead. The TMA has a thread of its own: when
 //     it shared a warp with the scale staging, the MMA threads waited for `full` most of the time.
 //   * A thread owns one output row: it stores whole 32-byte sectors (st.global.v8).
+//   * A stage is four groups (256 bytes of K, two TMA boxes per operand): the per-stage hand-offs (scale
+//     barrier, stage release) cost a fold warp some 270 cycles, so they are paid every fourth group.
 //
 // Per CTA (rank 0 = leader issues the MMAs for both), 24 warps:
 //   warp 0      one thread: TMA for own A rows and own B rows
-//   warps 1, 2  stage the scales (sw: the tile's 128 columns; sa: this CTA's 128 rows; two groups per stage)
+//   warps 1, 2  stage the scales (sw: the tile's 128 columns; sa: this CTA's 128 rows; four groups per stage)
 //   warps 4-7   leader only, one thread each: tcgen05.mma.cta_group::2 kind::f8f6f4 (two K = 32 steps
 //               per group) and the commit that arrives on both CTAs' barriers
 //   warps 8-23  fold this CTA's 128 rows x 128 columns, 32 rows x 32 columns per warp
@@ -47,10 +49,11 @@ constexpr int TEAMS = 2;       // independent fold pipelines, each with its own 
 constexpr int THREADS = 768;
 constexpr int BM = 128;        // rows per CTA; the pair covers 256
 constexpr int BN = 128;        // columns of the pair's tile; each CTA loads 64 of the B rows
-constexpr int STAGE_K = 128;   // bytes (= codes) of K per pipeline stage: two groups
+constexpr int STAGE_K = 256;   // bytes (= codes) of K per pipeline stage: four groups, as two 128-byte swizzle rows
+constexpr int STAGE_GROUPS = STAGE_K / 64, K_HALVES = STAGE_K / 128;
 constexpr int TEAM_COLUMNS = BN / TEAMS;
 constexpr int BUFFERS = 4;     // TMEM buffers of TEAM_COLUMNS fp32 columns per team
-constexpr int STAGES = 8;
+constexpr int STAGES = 4;
 constexpr int TURNS = 2;       // MMA-issuing threads per team, taking turns group by group
 constexpr int PRODUCER_WARP = 0, SW_WARP = 1, SA_WARP = 2, MMA_WARP0 = 4, MMA_WARPS = TURNS * TEAMS, FOLD_WARP0 = 8, FOLD_WARPS = 16;  // warp 3 idle
 static_assert(MMA_WARP0 + MMA_WARPS <= FOLD_WARP0, "the issuing threads sit in control warps");
@@ -69,12 +72,13 @@ static_assert(FOLD_WARP0 / 4 * CONTROL_REGISTERS + FOLD_WARPS / 4 * FOLD_REGISTE
 // Pause between polls of the roles that run stages ahead and therefore wait most of the time: a warp that spins
 // takes issue slots from the fold warps of its scheduler.
 constexpr uint32_t AHEAD_BACKOFF_NS = 256;
-constexpr int SCALE_AHEAD = 6, SCALE_RING = 8;  // stages of scales in flight; ring slots
+constexpr int SCALE_AHEAD = 3, SCALE_RING = 4;  // stages of scales in flight; ring slots
 
-constexpr int A_BYTES = BM * 128, B_BYTES = (BN / 2) * 128;
-constexpr int SW_BYTES = 2 * BN * 4;   // fp32 [group of the stage][column]
-constexpr int SA_BYTES = BM * 8;       // float2 [row] = (group 0, group 1)
-constexpr int RING_BYTES = SCALE_RING * (BN + BM) * 4;  // half2 per column / row and slot
+constexpr int A_HALF_BYTES = BM * 128, B_HALF_BYTES = (BN / 2) * 128;  // one 128-byte-wide slab of a stage
+constexpr int A_BYTES = K_HALVES * A_HALF_BYTES, B_BYTES = K_HALVES * B_HALF_BYTES;
+constexpr int SW_BYTES = STAGE_GROUPS * BN * 4;   // fp32 [group of the stage][column]
+constexpr int SA_BYTES = BM * 16;                 // float4 [row] = the stage's four groups
+constexpr int RING_BYTES = SCALE_RING * (BN + BM) * 8;  // four fp16 per column / row and slot
 constexpr int BARRIER_BYTES = 512;
 constexpr int SMEM_BYTES = STAGES * (A_BYTES + B_BYTES + SW_BYTES + SA_BYTES) + RING_BYTES + BARRIER_BYTES + 1024;
 static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
@@ -86,8 +90,8 @@ static_assert(BN == 128 && BM == 128, "the staging warp handles four columns and
 struct View {
     uint8_t *tile_a, *tile_b;
     float *sw_tile;
-    float2 *sa_tile;
-    __half2 *ring;
+    float4 *sa_tile;
+    uint2 *ring;
     uint64_t *full, *scale_ready, *empty, *dot_full, *dot_empty;
     uint32_t tmem_base, cta;
     int pair, pairs, tiles, tiles_m, k_stages, groups;
@@ -126,19 +130,23 @@ __device__ __forceinline__ void producer_role(const View &v, const CUtensorMap *
         const int n0 = walk.n_index * BN + static_cast<int>(v.cta) * B_BOX_ROWS;
         // the leader expects the bytes of both CTAs' loads on its barrier
         if (v.cta == 0) mbarrier_arrive_expect_tx(&v.full[s], 2 * (A_BYTES + B_BYTES));
-        tma_load_2d_pair(v.tile_a + s * A_BYTES, map_a, &v.full[s], walk.ks * STAGE_K, m0);
 #pragma unroll
-        for (int team = 0; team < TEAMS; ++team)  // this CTA's half of each team's columns
-            tma_load_2d_pair(v.tile_b + s * B_BYTES + team * (B_BOX_ROWS * 128), map_w, &v.full[s], walk.ks * STAGE_K,
-                             n0 + team * TEAM_COLUMNS);
+        for (int half = 0; half < K_HALVES; ++half) {
+            const int k0 = walk.ks * STAGE_K + half * 128;
+            tma_load_2d_pair(v.tile_a + s * A_BYTES + half * A_HALF_BYTES, map_a, &v.full[s], k0, m0);
+#pragma unroll
+            for (int team = 0; team < TEAMS; ++team)  // this CTA's half of each team's columns
+                tma_load_2d_pair(v.tile_b + s * B_BYTES + half * B_HALF_BYTES + team * (B_BOX_ROWS * 128), map_w, &v.full[s], k0,
+                                 n0 + team * TEAM_COLUMNS);
+        }
         if (++s == STAGES) s = 0, phase ^= 1;
     }
 }
 
 // Warps 1 and 2. Warp 1 stages the weight scales of the tile's 128 columns, warp 2 the activation scales of
-// this CTA's 128 rows: per stage the two groups' values (one half2 per column or row) are fetched
+// this CTA's 128 rows: per stage the four groups' values (8 bytes per column or row) are fetched
 // SCALE_AHEAD stages early with 4-byte cp.async and, when the stage is free again, written out as
-// fp32: sw[group][column] and sa[row] = (group 0, group 1).
+// fp32: sw[group][column] and sa[row] = (groups 0..3).
 template <bool ROWS>
 __device__ __forceinline__ void scale_role(const View &v, const __half *__restrict__ values, int limit, int lane) {
     constexpr int RING_OFFSET = ROWS ? BN : 0;
@@ -147,12 +155,12 @@ __device__ __forceinline__ void scale_role(const View &v, const __half *__restri
     auto fetch = [&]() {
         if (!ahead.done(v)) {
             const int first = ROWS ? ahead.m_index * 2 * BM + static_cast<int>(v.cta) * BM : ahead.n_index * BN;
-            __half2 *slot = v.ring + ahead_slot * (BN + BM) + RING_OFFSET + lane;
-            const __half *source = values + static_cast<size_t>(first + lane) * v.groups + 2 * ahead.ks;
+            uint2 *slot = v.ring + ahead_slot * (BN + BM) + RING_OFFSET + lane;
+            const __half *source = values + static_cast<size_t>(first + lane) * v.groups + STAGE_GROUPS * ahead.ks;
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                if (first + p * 32 + lane < limit) cp_async_4(slot + p * 32, source + static_cast<size_t>(p * 32) * v.groups);
-                else slot[p * 32] = __halves2half2(__ushort_as_half(0), __ushort_as_half(0));
+                if (first + p * 32 + lane < limit) cp_async_8(slot + p * 32, source + static_cast<size_t>(p * 32) * v.groups);
+                else slot[p * 32] = make_uint2(0u, 0u);
             }
             ahead.next(v);
         }
@@ -164,21 +172,28 @@ __device__ __forceinline__ void scale_role(const View &v, const __half *__restri
     for (StageWalk walk(v); !walk.done(v); walk.next(v)) {
         fetch();
         cp_async_wait<SCALE_AHEAD>();  // this thread's copies for this stage have landed
-        const __half2 *slot = v.ring + slot_index * (BN + BM) + RING_OFFSET + lane;
-        float2 pair[4];
+        const uint2 *slot = v.ring + slot_index * (BN + BM) + RING_OFFSET + lane;
+        float4 quad[4];  // [p] = the four groups' scales of column / row p * 32 + lane
 #pragma unroll
-        for (int p = 0; p < 4; ++p) pair[p] = __half22float2(slot[p * 32]);
+        for (int p = 0; p < 4; ++p) {
+            const uint2 raw = slot[p * 32];
+            const float2 low = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+            const float2 high = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+            quad[p] = make_float4(low.x, low.y, high.x, high.y);
+        }
         if (!mbarrier_wait_warp(&v.empty[s], phase ^ 1, &g_status, STATUS_WAIT_EMPTY | 0x6000 | s, lane, AHEAD_BACKOFF_NS)) break;
         if (ROWS) {
-            float2 *sa_stage = v.sa_tile + s * BM + lane;
+            float4 *sa_stage = v.sa_tile + s * BM + lane;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) sa_stage[p * 32] = pair[p];
+            for (int p = 0; p < 4; ++p) sa_stage[p * 32] = quad[p];
         } else {
-            float *sw_stage = v.sw_tile + s * 2 * BN + lane;
+            float *sw_stage = v.sw_tile + s * STAGE_GROUPS * BN + lane;
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                sw_stage[p * 32] = pair[p].x;
-                sw_stage[BN + p * 32] = pair[p].y;
+                sw_stage[p * 32] = quad[p].x;
+                sw_stage[BN + p * 32] = quad[p].y;
+                sw_stage[2 * BN + p * 32] = quad[p].z;
+                sw_stage[3 * BN + p * 32] = quad[p].w;
             }
         }
         __syncwarp();
@@ -191,7 +206,7 @@ __device__ __forceinline__ void scale_role(const View &v, const __half *__restri
 
 // Warps 4-7 of the leader, one thread each. Thread `mine` serves team (mine % TEAMS) and multiplies the
 // groups whose running number is (mine / TEAMS) modulo TURNS into that team's TMEM buffers: N = 64
-// columns per MMA. A group's number fixes everything else: its pipeline stage (two groups per stage) and
+// columns per MMA. A group's number fixes everything else: its pipeline stage (four groups per stage, in two 128-byte slabs) and
 // its buffer.
 __device__ __forceinline__ void mma_role(const View &v, uint32_t mine) {
     constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * BM, TEAM_COLUMNS);
@@ -200,14 +215,14 @@ __device__ __forceinline__ void mma_role(const View &v, uint32_t mine) {
     const uint32_t team = mine % TEAMS, turn = mine / TEAMS;
     uint64_t *dot_full = v.dot_full + team * BUFFERS, *dot_empty = v.dot_empty + team * BUFFERS;
     for (uint32_t group = turn; group < total_groups; group += TURNS) {
-        const uint32_t iteration = group >> 1, gl = group & 1;
+        const uint32_t iteration = group / STAGE_GROUPS, half = (group % STAGE_GROUPS) >> 1, gl = group & 1;
         const uint32_t s = iteration % STAGES, phase = (iteration / STAGES) & 1;
         const uint32_t buffer = group % BUFFERS, buffer_phase = (group / BUFFERS) & 1;
         if (!mbarrier_wait(&v.full[s], phase, &g_status, STATUS_WAIT_FULL | 0x5000 | s)) break;
         if (!mbarrier_wait(&dot_empty[buffer], buffer_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x5000 | buffer)) break;
         tcgen05_fence_after();
-        const uint32_t a_address = smem_u32(v.tile_a + s * A_BYTES) + gl * 64;
-        const uint32_t b_address = smem_u32(v.tile_b + s * B_BYTES + team * (B_BOX_ROWS * 128)) + gl * 64;
+        const uint32_t a_address = smem_u32(v.tile_a + s * A_BYTES + half * A_HALF_BYTES) + gl * 64;
+        const uint32_t b_address = smem_u32(v.tile_b + s * B_BYTES + half * B_HALF_BYTES + team * (B_BOX_ROWS * 128)) + gl * 64;
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk)
             umma_f8_pair(v.tmem_base + (team * BUFFERS + buffer) * TEAM_COLUMNS, umma_desc_k_sw128(a_address + kk * 32),
@@ -247,10 +262,10 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
             const int s = iteration % STAGES;
             const uint32_t phase = (iteration / STAGES) & 1;
             if (!mbarrier_wait_warp(&v.scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x5000 | s, lane)) { alive = false; break; }
-            const float *sw_stage = v.sw_tile + s * 2 * BN + slice * COLUMNS;
-            const float2 sa_pair = v.sa_tile[s * BM + quadrant * 32 + lane];
+            const float *sw_stage = v.sw_tile + s * STAGE_GROUPS * BN + slice * COLUMNS;
+            const float4 sa_quad = v.sa_tile[s * BM + quadrant * 32 + lane];
 #pragma unroll
-            for (int gl = 0; gl < 2; ++gl, ++group_count) {
+            for (int gl = 0; gl < STAGE_GROUPS; ++gl, ++group_count) {
                 const uint32_t buffer = group_count % BUFFERS;
                 if (!mbarrier_wait_warp(const_cast<uint64_t *>(&dot_full[buffer]), (group_count / BUFFERS) & 1, &g_status,
                                         STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane)) { alive = false; break; }
@@ -265,10 +280,10 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
 #pragma unroll
                     for (int j = 0; j < COLUMNS; ++j)
                         if (n0 + j < shape.n)
-                            dots_out[(static_cast<size_t>(row) * shape.n + n0 + j) * v.groups + ks * 2 + gl] =
+                            dots_out[(static_cast<size_t>(row) * shape.n + n0 + j) * v.groups + ks * STAGE_GROUPS + gl] =
                                 static_cast<int32_t>(__uint_as_float(dots[j]));
                 }
-                const float scale = gl == 0 ? sa_pair.x : sa_pair.y;
+                const float scale = gl == 0 ? sa_quad.x : gl == 1 ? sa_quad.y : gl == 2 ? sa_quad.z : sa_quad.w;
                 const uint64_t sa2 = pack_f32x2(scale, scale);
                 const float *sw_group = sw_stage + gl * BN;
 #pragma unroll
@@ -343,8 +358,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint8_t *tile_a = smem;
     uint8_t *tile_b = tile_a + STAGES * A_BYTES;
     float *sw_tile = reinterpret_cast<float *>(tile_b + STAGES * B_BYTES);
-    float2 *sa_tile = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(sw_tile) + STAGES * SW_BYTES);
-    __half2 *ring = reinterpret_cast<__half2 *>(reinterpret_cast<uint8_t *>(sa_tile) + STAGES * SA_BYTES);
+    float4 *sa_tile = reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(sw_tile) + STAGES * SW_BYTES);
+    uint2 *ring = reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(sa_tile) + STAGES * SA_BYTES);
     uint64_t *full = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(ring) + RING_BYTES);
     uint64_t *scale_ready = full + STAGES;
     uint64_t *empty = scale_ready + STAGES;
