@@ -250,7 +250,10 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
     const uint32_t tmem_lane = v.tmem_base + team * BUFFERS * TEAM_COLUMNS + (slice % (TEAM_COLUMNS / COLUMNS)) * COLUMNS +
                                (static_cast<uint32_t>(quadrant * 32) << 16);
     uint32_t dots[COLUMNS];  // dots[j] = dot of this thread's row and column j of the warp's 32
-    bool alive = true;
+    // Waits are per lane (one try_wait when the phase is complete, which it mostly is) and the warp re-converges
+    // at a __syncwarp; a vote on the outcome would add 30 cycles to every group. A lane whose wait ran out of time
+    // sets `failed`; the warp looks at it together once per stage.
+    bool alive = true, failed = false;
     uint32_t iteration = 0, group_count = 0;
     for (int tile = v.pair; tile < v.tiles && alive; tile += v.pairs) {
         const int row = (tile % v.tiles_m) * 2 * BM + static_cast<int>(v.cta) * BM + quadrant * 32 + lane;
@@ -261,14 +264,17 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
         for (int ks = 0; ks < v.k_stages && alive; ++ks, ++iteration) {
             const int s = iteration % STAGES;
             const uint32_t phase = (iteration / STAGES) & 1;
-            if (!mbarrier_wait_warp(&v.scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x5000 | s, lane)) { alive = false; break; }
+            if (__any_sync(0xffffffffu, failed)) { alive = false; break; }
+            failed = !mbarrier_wait(&v.scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x5000 | s);
+            __syncwarp();
             const float *sw_stage = v.sw_tile + s * STAGE_GROUPS * BN + slice * COLUMNS;
             const float4 sa_quad = v.sa_tile[s * BM + quadrant * 32 + lane];
 #pragma unroll
             for (int gl = 0; gl < STAGE_GROUPS; ++gl, ++group_count) {
                 const uint32_t buffer = group_count % BUFFERS;
-                if (!mbarrier_wait_warp(const_cast<uint64_t *>(&dot_full[buffer]), (group_count / BUFFERS) & 1, &g_status,
-                                        STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane)) { alive = false; break; }
+                failed |= !mbarrier_wait(const_cast<uint64_t *>(&dot_full[buffer]), (group_count / BUFFERS) & 1, &g_status,
+                                         STATUS_WAIT_TMEM_FULL | 0x5000 | buffer);
+                __syncwarp();
                 tcgen05_fence_after();
                 tmem_load_32x32(tmem_lane + buffer * TEAM_COLUMNS, dots);
                 tmem_load_wait();
