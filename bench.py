@@ -44,8 +44,8 @@ METRIC = "packed W4A4/W4A16 GEMM TOPS at M=4096 block shapes, % of tensor/HBM ro
 UNIT = "TOPS"
 WORKLOAD = "qwen-image MMDiT block image stream, W4A4 H256 g64, M=4096 hidden=3072: qkv 3072->9216, out 3072->3072, fc1 3072->12288, fc2 12288->3072"
 CPU_SAMPLE_ROWS = 256
-# DRAM bytes of one w4a4_pair::gemm_kernel launch of average size (42.3 MB read + 36.3 MB written), from ncu
-NCU_TRAFFIC_BYTES_PER_AVERAGE_LAUNCH = 78.6e6
+# DRAM bytes of one w4a4_pair::gemm_kernel launch of average size (42.3 MB read + 36.5 MB written), from ncu
+NCU_TRAFFIC_BYTES_PER_AVERAGE_LAUNCH = 78.8e6
 
 
 def measured_peaks():
