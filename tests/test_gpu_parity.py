@@ -236,6 +236,26 @@ def test_w4a16_gemv_matches_oracle(qi, m, n, k, kind):
     assert distance <= FP16_STORE_ULPS
 
 
+@pytest.mark.parametrize("m", [1, 3])
+def test_w4a16_gemv_scales_of_every_size(qi, m):
+    # scales from fp16 denormals up to 4: the GEMV's unpack treats scale >= 1/16 (where scale * 2^20 leaves fp16)
+    # and denormal scales on paths of their own; every one must give the reference's weights
+    n, k = 512, 1024
+    rng = np.random.default_rng(3100 + m)
+    codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    exponents = rng.integers(-20, 3, size=(n, k // 64)).astype(np.float32)
+    scales = (np.exp2(exponents) * rng.uniform(1.0, 2.0, size=exponents.shape)).astype(np.float16)
+    scales[::7, ::3] = np.float16(0.0)
+    minimums = (-7.5 * scales.astype(np.float32)).astype(np.float16)
+    x16 = qt.make_activations(rng, m, k, "silu")
+    expected = qo.w4a16_gemm(x16, codes, scales.view(np.uint16), minimums.view(np.uint16))
+    y = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    assert qi.w4a16_gemv_ex(up(x16), up(codes), up(scales.view(np.uint16)), up(minimums.view(np.uint16)), None, y,
+                            qi.DTYPE_F32, n, m, n, k) == 0
+    torch.cuda.synchronize()
+    assert qt.max_relative_error(y.cpu().numpy(), expected) <= OUTPUT_TOLERANCE
+
+
 # ---- W4A4 ----------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 256), (256, 384, 512), (128, 256, 3072), (384, 128, 1280)])
