@@ -273,6 +273,29 @@ def run_b200(args):
         }
         del w_codes, w_scales
         layers.append(layer)
+    # Without the all-gather: every rank holds every linear's whole output, all of them in ONE allocation that the
+    # other ranks map, and the GEMM's epilogue stores its slice into every rank's copy (buffer 0: the device-timed
+    # loop; 1 and 2: the end-to-end path's two slots).
+    fused = context is not None and args.gather == "fused" and args.w4a4_path == "wide"
+    peers = None
+    if fused:
+        sizes = [(m * layer["n"] * 2 + 255) // 256 * 256 for layer in layers]
+        pool = torch.empty(3 * sum(sizes), dtype=torch.uint8, device=device)
+
+        def exchange(item):
+            items = [None] * world
+            dist.all_gather_object(items, item)
+            return items
+
+        peers = qi.PeerOutput(context, pool, exchange)
+        offset = 0
+        for layer, size in zip(layers, sizes):
+            layer["lo"] = qi.shard_plan(layer["n"], world, rank)[0]
+            layer["whole"], layer["copies"] = [], []
+            for _ in range(3):
+                layer["whole"].append(pool[offset:offset + m * layer["n"] * 2].view(torch.float16).view(m, layer["n"]))
+                layer["copies"].append(peers.copies(offset))
+                offset += size
     torch.cuda.synchronize()
 
     launches = {"count": 0}
@@ -296,7 +319,12 @@ def run_b200(args):
             if record_gemm_events is not None:
                 start = torch.cuda.Event(enable_timing=True)
                 start.record(stream)
-            if args.w4a4_path == "wide":
+            if fused:
+                status = qi.w4a4_gemm_wide_scatter_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
+                                                      None, layer["copies"][0 if slot is None else slot + 1],
+                                                      (rank + 1) % world, qi.DTYPE_F16, layer["n"], layer["lo"], m,
+                                                      n_local, k, stream_handle)
+            elif args.w4a4_path == "wide":
                 status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
                                               None, y_out, qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
             else:
@@ -313,7 +341,10 @@ def run_b200(args):
                 computed_event = torch.cuda.Event()
                 computed_event.record(stream)
                 gather_stream.wait_event(computed_event)
-                status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, gather_stream.cuda_stream)
+                if fused:  # the slices are already on their way: what is left is to know that every rank's have landed
+                    status = context.barrier(gather_stream.cuda_stream)
+                else:
+                    status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, gather_stream.cuda_stream)
                 assert status == 0, f"all-gather {layer['name']}: status {status}"
                 layer["gathered"] = torch.cuda.Event()
                 layer["gathered"].record(gather_stream)
@@ -330,6 +361,18 @@ def run_b200(args):
         step()
     barrier()
     assert qi.kernel_status() == 0, "a kernel gave up on a wait during warm-up"
+    if fused:
+        # every rank's whole outputs, as its peers wrote them, equal what the all-gather of the slices gives
+        for layer in layers:
+            status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"], None,
+                                          layer["y_local"], qi.DTYPE_F16, layer["n_local"], m, layer["n_local"],
+                                          layer["k"], stream_handle)
+            assert status == 0
+            assert context.all_gather(layer["y_local"], layer["y_all"], qi.DTYPE_F16, m, layer["n_local"], stream_handle) == 0
+            stream.synchronize()
+            gathered = layer["y_all"].permute(1, 0, 2).reshape(m, layer["n"])
+            assert torch.equal(gathered, layer["whole"][0]), f"{layer['name']}: the peers' stores differ from the all-gather"
+        barrier()
 
     # ---- device-timed region: exactly `steps` steps
     launches["count"] = 0
@@ -380,7 +423,10 @@ def run_b200(args):
         out_stream.wait_event(computed[slot])
         with torch.cuda.stream(out_stream):
             for layer, hy in zip(layers, host_y):
-                hy.copy_(layer["y_slots"][slot], non_blocking=True)
+                if fused:  # this rank's slice of its whole output
+                    hy.copy_(layer["whole"][slot + 1][:, layer["lo"]:layer["lo"] + layer["n_local"]], non_blocking=True)
+                else:
+                    hy.copy_(layer["y_slots"][slot], non_blocking=True)
         copied_out[slot] = torch.cuda.Event()
         copied_out[slot].record(out_stream)
 
@@ -421,7 +467,8 @@ def run_b200(args):
             "data": "synthetic: W ~ N(0,0.02) rotated (H256) and quantised to int4 g64 on the device, "
                     "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
             "config": {"workload": WORKLOAD, "m": m, "ops_per_step": OPS_PER_STEP, "w4a4_path": args.w4a4_path,
-                       "parallelism": "single GPU" if world == 1 else f"N-sharded x{world} + all-gather",
+                       "parallelism": "single GPU" if world == 1 else (f"N-sharded x{world}, slices stored to every GPU by the GEMM epilogue + barrier" if fused
+                                                                              else f"N-sharded x{world} + NCCL all-gather"),
                        "outputs": "fp16", "l2": f"per-step working set {working_set / 1e6:.0f} MB per GPU exceeds the 126 MB L2"},
             "gpu_launches": timed_launches,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -440,6 +487,9 @@ def run_b200(args):
             result["other_kernels"] = other_kernels(qi, torch, device, stream, peaks, m)
     if dist is not None:
         torch.cuda.synchronize()
+        dist.barrier()  # nobody unmaps a copy that another rank may still write
+        if peers is not None:
+            peers.close()
         context.destroy()
         dist.barrier()
         dist.destroy_process_group()
@@ -510,6 +560,9 @@ def main():
     parser.add_argument("--w4a4-path", default="wide", choices=["packed", "wide"],
                         help="packed: the drop-in kernels on nibble-packed codes (int8 tensor-core dots); "
                              "wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
+    parser.add_argument("--gather", default="nccl", choices=["fused", "nccl"],
+                        help="N > 1: how the column slices reach every GPU. fused: the GEMM's epilogue stores its slice "
+                             "into every GPU's output over NVLink, a barrier follows; nccl: an all-gather after each GEMM")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

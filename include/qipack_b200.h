@@ -185,6 +185,34 @@ int qi_shard_linear(void *context, const qi_packed_linear *local_record, const q
                     const void *input, int input_dtype, void *y_local, void *y_slabs, int output_dtype, int rows,
                     int reuse_input, void *stream);
 
+/* The W4A4 linear without the all-gather: every rank holds the whole output y [rows, N] and the
+ * GEMM stores its slice into every rank's copy itself, over NVLink, from its epilogue.
+ *
+ * qi_shard_peer_export: `pointer` lies in a cudaMalloc allocation of this process; `handle`
+ * (QI_SHARD_PEER_HANDLE_BYTES bytes) and `offset` name it for the other processes of the box, which
+ * the caller reaches by any host channel. qi_shard_peer_open, in another process with its own
+ * device current, maps that allocation (peer access is enabled on the way) and returns the same
+ * address there; qi_shard_peer_close unmaps it. An allocation is opened once per process: carve
+ * several outputs out of one allocation on the host. */
+#define QI_SHARD_PEER_HANDLE_BYTES 64
+int qi_shard_peer_export(const void *pointer, void *handle, size_t *offset);
+int qi_shard_peer_open(const void *handle, size_t offset, void **pointer);
+int qi_shard_peer_close(void *pointer, size_t offset);
+
+/* y_copies[c][row * ldy + column + j] <- (A . W^T)[row][j] for every copy c < copies (at most 8):
+ * qi_w4a4_gemm_wide_ex with the output written to `copies` matrices of the same layout, one of
+ * them usually this rank's own and the others peer mappings; `column` (a multiple of 32) is where
+ * this rank's slice starts, and a CTA stores to copy first_copy first (give each rank another one).
+ * k must be a multiple of 256. The stores of a launch are complete when the launch is: a consumer
+ * on another rank waits for qi_shard_barrier, placed after the launch in stream order. */
+int qi_w4a4_gemm_wide_scatter_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                                 const float *bias, void *const *y_copies, int copies, int first_copy, int y_dtype,
+                                 long long ldy, int column, int m, int n, int k, void *stream);
+
+/* Every rank's work queued on its `stream` before this call has completed when the call's own work
+ * completes on any rank's stream (a four-byte NCCL all-reduce). */
+int qi_shard_barrier(void *context, void *stream);
+
 /* ---- diagnostics --------------------------------------------------------------------------- */
 
 /* Kernels of this library never spin without a bound: a wait that runs out records a code

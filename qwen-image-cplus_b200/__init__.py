@@ -84,6 +84,12 @@ SIGNATURES = {
     "qi_shard_destroy": [_P],
     "qi_shard_rank": [_P, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
     "qi_shard_all_gather": [_P, _P, _P, _I, _I, _I, _P],
+    "qi_shard_barrier": [_P, _P],
+    "qi_shard_peer_export": [_P, _P, ctypes.POINTER(ctypes.c_size_t)],
+    "qi_shard_peer_open": [_P, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)],
+    "qi_shard_peer_close": [_P, ctypes.c_size_t],
+    "qi_w4a4_gemm_wide_scatter_ex": [_P, _P, _P, _P, _P, ctypes.POINTER(ctypes.c_void_p), _I, _I, _I, _LL, _I, _I, _I,
+                                     _I, _P],
     "qi_shard_linear": [_P, ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _P, _I, _I,
                         _I, _P],
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
@@ -284,6 +290,9 @@ class ShardContext:
     def all_gather(self, y_local, y_slabs, output_dtype: int, rows: int, n_local: int, stream=None) -> int:
         return lib().qi_shard_all_gather(self.handle, _p(y_local), _p(y_slabs), output_dtype, rows, n_local, _p(stream))
 
+    def barrier(self, stream=None) -> int:
+        return lib().qi_shard_barrier(self.handle, _p(stream))
+
     def linear(self, model: PackedLinear, work: LinearWork, input, y_local, y_slabs, rows: int,
                reuse_input: bool = False, *, input_dtype: int = DTYPE_F32, output_dtype: int = DTYPE_F32,
                stream=None) -> int:
@@ -297,3 +306,53 @@ class ShardContext:
             self.handle = ctypes.c_void_p(0)
             return status
         return 0
+
+
+SHARD_PEER_HANDLE_BYTES = 64
+
+
+class PeerOutput:
+    """The same device buffer on every rank of the box, each rank holding addresses of all copies.
+
+    `local` is this rank's buffer (anything with data_ptr(), carved out of ONE cudaMalloc allocation
+    that is exported once); `exchange(item) -> list` carries a picklable item to every rank and returns
+    all ranks' items in rank order (torch.distributed.all_gather_object, for instance). Collective."""
+
+    def __init__(self, context: ShardContext, local, exchange):
+        handle = ctypes.create_string_buffer(SHARD_PEER_HANDLE_BYTES)
+        offset = ctypes.c_size_t(0)
+        status = lib().qi_shard_peer_export(_p(local), handle, ctypes.byref(offset))
+        if status != 0:
+            raise RuntimeError(f"qi_shard_peer_export: status {status}")
+        everyone = exchange((handle.raw, offset.value))
+        if len(everyone) != context.ranks:
+            raise RuntimeError("exchange() must return one item per rank")
+        self.rank, self.ranks = context.rank, context.ranks
+        self.addresses, self._opened = [], []
+        for rank, (raw, peer_offset) in enumerate(everyone):
+            if rank == context.rank:
+                self.addresses.append(_p(local).value)
+                continue
+            pointer = ctypes.c_void_p(0)
+            status = lib().qi_shard_peer_open(ctypes.create_string_buffer(raw, SHARD_PEER_HANDLE_BYTES), peer_offset,
+                                              ctypes.byref(pointer))
+            if status != 0:
+                raise RuntimeError(f"qi_shard_peer_open (rank {rank}): status {status}")
+            self.addresses.append(pointer.value)
+            self._opened.append((pointer.value, peer_offset))
+
+    def copies(self, byte_offset: int = 0):
+        """A C array of every rank's address of the byte `byte_offset` of the buffer."""
+        return (ctypes.c_void_p * self.ranks)(*[address + byte_offset for address in self.addresses])
+
+    def close(self) -> None:
+        for address, offset in self._opened:
+            lib().qi_shard_peer_close(ctypes.c_void_p(address), offset)
+        self._opened = []
+
+
+def w4a4_gemm_wide_scatter_ex(a_bytes, a_scales, w_bytes, w_scales, bias, copies, first_copy: int, y_dtype: int,
+                              ldy: int, column: int, m: int, n: int, k: int, stream=None) -> int:
+    """`copies`: what PeerOutput.copies() returns (keep it alive until the call returns)."""
+    return lib().qi_w4a4_gemm_wide_scatter_ex(_p(a_bytes), _p(a_scales), _p(w_bytes), _p(w_scales), _p(bias), copies,
+                                              len(copies), first_copy, y_dtype, ldy, column, m, n, k, _p(stream))

@@ -192,7 +192,8 @@ int launch_w4a4_wide(const void *a_bytes, const void *a_scales, const void *w_by
 int g_w4a4_wide_single = 0;
 
 int launch_w4a4_pair(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
-                     const float *bias, void *y, int32_t *dots, const GemmShape &shape, cudaStream_t stream, int device) {
+                     const float *bias, void *y, int32_t *dots, const GemmShape &shape, cudaStream_t stream, int device,
+                     const w4a4_pair::PeerOutputs *peers = nullptr) {
     namespace wp = w4a4_pair;
     CUtensorMap map_a, map_w;
     if (!make_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_bytes, shape.k, shape.m, static_cast<uint64_t>(shape.k),
@@ -201,18 +202,23 @@ int launch_w4a4_pair(const void *a_bytes, const void *a_scales, const void *w_by
     if (!make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_bytes, shape.k, shape.n, static_cast<uint64_t>(shape.k),
                   128, wp::B_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B))
         return INVALID;
-    auto kernel = dots != nullptr ? wp::gemm_kernel<true> : wp::gemm_kernel<false>;
-    static bool configured[MAX_DEVICES][2];
-    if (!configured[device][dots != nullptr]) {
+    if (peers != nullptr && dots != nullptr) return INVALID;
+    const int variant = peers != nullptr ? 2 : (dots != nullptr ? 1 : 0);
+    auto kernel = variant == 2 ? wp::gemm_kernel<false, true>
+                               : (variant == 1 ? wp::gemm_kernel<true, false> : wp::gemm_kernel<false, false>);
+    static bool configured[MAX_DEVICES][3];
+    if (!configured[device][variant]) {
         const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wp::SMEM_BYTES);
         if (error != cudaSuccess) return static_cast<int>(error);
-        configured[device][dots != nullptr] = true;
+        configured[device][variant] = true;
     }
+    const wp::PeerOutputs outputs = peers != nullptr ? *peers : wp::PeerOutputs{};
     const int tiles = ((shape.m + 2 * wp::BM - 1) / (2 * wp::BM)) * ((shape.n + wp::BN - 1) / wp::BN);
     const int pairs = sm_count(device) / 2;
     const int grid = 2 * (tiles < pairs ? tiles : pairs);  // the kernel carries __cluster_dims__(2, 1, 1)
     kernel<<<grid, wp::THREADS, wp::SMEM_BYTES, stream>>>(map_a, map_w, static_cast<const __half *>(a_scales),
-                                                          static_cast<const __half *>(w_scales), bias, y, dots, shape);
+                                                          static_cast<const __half *>(w_scales), bias, y, dots, shape,
+                                                          outputs);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -369,6 +375,36 @@ int qi_w4a4_gemm_wide_ex(const void *a_bytes, const void *a_scales, const void *
                          const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
     return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k,
                           static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a4_gemm_wide_scatter_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                                 const float *bias, void *const *y_copies, int copies, int first_copy, int y_dtype,
+                                 long long ldy, int column, int m, int n, int k, void *stream) {
+    namespace wp = w4a4_pair;
+    if (y_copies == nullptr || copies < 1 || copies > wp::MAX_PEERS || first_copy < 0 || first_copy >= copies)
+        return INVALID;
+    if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % wp::STAGE_K != 0 || column < 0 || column % 32 != 0) return INVALID;
+    if (!a_bytes || !a_scales || !w_bytes || !w_scales) return INVALID;
+    if (!aligned16(a_bytes) || !aligned16(w_bytes) || (reinterpret_cast<uintptr_t>(a_scales) & 3) ||
+        (reinterpret_cast<uintptr_t>(w_scales) & 3))
+        return INVALID;
+    if (y_dtype != QI_DTYPE_F16 && y_dtype != QI_DTYPE_F32) return INVALID;
+    if (ldy < static_cast<long long>(column) + n) return INVALID;
+    const size_t element = y_dtype == QI_DTYPE_F16 ? 2 : 4;
+    wp::PeerOutputs outputs = {};
+    outputs.count = copies;
+    outputs.first = first_copy;
+    for (int i = 0; i < copies; ++i) {
+        if (y_copies[i] == nullptr) return INVALID;
+        outputs.y[i] = static_cast<char *>(y_copies[i]) + static_cast<size_t>(column) * element;
+        if (!output_ok(outputs.y[i], y_dtype, ldy, n) || (reinterpret_cast<uintptr_t>(outputs.y[i]) & 31)) return INVALID;
+    }
+    if ((ldy * static_cast<long long>(element)) % 32 != 0) return INVALID;  // the epilogue stores whole 32-byte sectors
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
+    return launch_w4a4_pair(a_bytes, a_scales, w_bytes, w_scales, bias, outputs.y[first_copy], nullptr, shape,
+                            static_cast<cudaStream_t>(stream), device, &outputs);
 }
 
 int qi_w4a4_group_dots_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,

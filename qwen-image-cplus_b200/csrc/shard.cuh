@@ -4,6 +4,12 @@
 // are all-gathered over NVLink with NCCL. The reference is single-GPU (runtime.cu:6-19 uses device
 // 0 only); this is new work with no counterpart there.
 //
+// The W4A4 linear has a second form without the all-gather: every rank holds the whole [m, N]
+// output, the ranks map one another's copy (CUDA IPC, qi_shard_peer_export / _open), and the GEMM's
+// epilogue stores its slice into every copy itself (qi_w4a4_gemm_wide_scatter_ex). What is left of
+// the collective is qi_shard_barrier: a kernel's stores are complete when it ends, so once every
+// rank has passed a barrier placed after its GEMM in stream order, every copy is whole.
+//
 // One process per GPU. NCCL is not linked: it is looked up at run time (dlopen), so that a process
 // that already carries an NCCL (a PyTorch process, for instance) shares that copy and a
 // single-GPU user of this library needs none at all.
@@ -60,7 +66,23 @@ struct Context {
     uint32_t magic;
     int rank, ranks, device;
     void *comm;
+    float *token;  // four bytes for the barrier's all-reduce; allocated by the first barrier
 };
+
+typedef CUresult (*AddressRange)(CUdeviceptr *, size_t *, CUdeviceptr);
+
+inline AddressRange address_range() {
+    static AddressRange function = nullptr;
+    if (function == nullptr) {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            function = reinterpret_cast<AddressRange>(entry);
+    }
+    return function;
+}
+static_assert(sizeof(cudaIpcMemHandle_t) == QI_SHARD_PEER_HANDLE_BYTES, "size of an exported handle");
 constexpr uint32_t CONTEXT_MAGIC = 0x51495348;  // "QISH"
 
 inline Context *checked(void *context) {
@@ -106,7 +128,7 @@ int qi_shard_create(void **context, int rank, int ranks, const void *id) {
     int device = 0;
     cudaError_t error = cudaGetDevice(&device);
     if (error != cudaSuccess) return static_cast<int>(error);
-    Context *c = new Context{CONTEXT_MAGIC, rank, ranks, device, nullptr};
+    Context *c = new Context{CONTEXT_MAGIC, rank, ranks, device, nullptr, nullptr};
     UniqueId unique;
     memcpy(&unique, id, sizeof(unique));
     const int result = api.CommInitRank(&c->comm, ranks, unique, rank);
@@ -123,6 +145,7 @@ int qi_shard_destroy(void *context) {
     Context *c = checked(context);
     if (c == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     const int result = c->comm ? nccl().CommDestroy(c->comm) : 0;
+    if (c->token != nullptr) cudaFree(c->token);
     c->magic = 0;
     delete c;
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
@@ -148,6 +171,56 @@ int qi_shard_all_gather(void *context, const void *y_local, void *y_slabs, int o
     const int result = nccl().AllGather(y_local, y_slabs, count, output_dtype == QI_DTYPE_F16 ? NCCL_FLOAT16 : NCCL_FLOAT32,
                                         c->comm, static_cast<cudaStream_t>(stream));
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
+int qi_shard_barrier(void *context, void *stream) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    if (c->ranks == 1) return 0;
+    if (nccl().AllReduce == nullptr) return NCCL_MISSING;
+    if (c->token == nullptr) {
+        cudaError_t error = cudaMalloc(&c->token, sizeof(float));
+        if (error == cudaSuccess) error = cudaMemset(c->token, 0, sizeof(float));
+        if (error != cudaSuccess) return static_cast<int>(error);
+    }
+    const int result = nccl().AllReduce(c->token, c->token, 1, NCCL_FLOAT32, 0 /* ncclSum */, c->comm,
+                                        static_cast<cudaStream_t>(stream));
+    return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
+int qi_shard_peer_export(const void *pointer, void *handle, size_t *offset) {
+    using namespace qi::shard;
+    if (pointer == nullptr || handle == nullptr || offset == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    AddressRange range = address_range();
+    if (range == nullptr) return static_cast<int>(cudaErrorNotSupported);
+    CUdeviceptr base = 0;
+    size_t bytes = 0;
+    if (range(&base, &bytes, reinterpret_cast<CUdeviceptr>(pointer)) != CUDA_SUCCESS)
+        return static_cast<int>(cudaErrorInvalidValue);
+    cudaIpcMemHandle_t exported;
+    const cudaError_t error = cudaIpcGetMemHandle(&exported, reinterpret_cast<void *>(base));
+    if (error != cudaSuccess) return static_cast<int>(error);
+    memcpy(handle, &exported, sizeof(exported));
+    *offset = reinterpret_cast<CUdeviceptr>(pointer) - base;
+    return 0;
+}
+
+int qi_shard_peer_open(const void *handle, size_t offset, void **pointer) {
+    if (handle == nullptr || pointer == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    *pointer = nullptr;
+    cudaIpcMemHandle_t imported;
+    memcpy(&imported, handle, sizeof(imported));
+    void *base = nullptr;
+    const cudaError_t error = cudaIpcOpenMemHandle(&base, imported, cudaIpcMemLazyEnablePeerAccess);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    *pointer = static_cast<char *>(base) + offset;
+    return 0;
+}
+
+int qi_shard_peer_close(void *pointer, size_t offset) {
+    if (pointer == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(cudaIpcCloseMemHandle(static_cast<char *>(pointer) - offset));
 }
 
 int qi_shard_linear(void *context, const qi_packed_linear *local_record, const qi_linear_work *work, const void *input,

@@ -86,6 +86,17 @@ static_assert((3 * STAGES + 2 * TEAMS * BUFFERS) * 8 + 8 <= BARRIER_BYTES, "barr
 constexpr int B_BOX_ROWS = TEAM_COLUMNS / 2;  // rows of B per TMA load: one CTA's half of one team's columns
 static_assert(BN == 128 && BM == 128, "the staging warp handles four columns and four rows per lane");
 
+// Where a column-sharded linear puts its slice: the same [m, ldy] matrix on every GPU of the box,
+// each one's copy reached through a peer mapping of its memory. The epilogue stores the tile into
+// every copy (plain st.global; the stores to the other GPUs travel over NVLink while the next
+// tiles are computed), so that no separate all-gather follows the kernel. `first` is the copy a
+// CTA starts with: each rank starts with another GPU, so that they do not all write to one at once.
+constexpr int MAX_PEERS = 8;
+struct PeerOutputs {
+    void *y[MAX_PEERS];
+    int count, first;
+};
+
 // Everything a role needs to find its way around the CTA's shared memory and the problem.
 struct View {
     uint8_t *tile_a, *tile_b;
@@ -239,8 +250,9 @@ __device__ __forceinline__ void mma_role(const View &v, uint32_t mine) {
 // All lanes need the same weight scales: one 16-byte broadcast load per four columns.
 // The arithmetic is the packed fp32 pair form of  acc = fma(dot, sa * sw, acc): each half is
 // IEEE-rounded exactly like the scalar instruction, so the result has the reference's bits.
-template <bool DUMP_DOTS>
+template <bool DUMP_DOTS, bool SCATTER>
 __device__ __forceinline__ void fold_role(const View &v, const float *__restrict__ bias, void *__restrict__ y,
+                                          const PeerOutputs &peers,
                                           int32_t *__restrict__ dots_out, const GemmShape &shape, int warp, int lane) {
     static_assert(COLUMNS == 32, "one tcgen05.ld.32x32b.x32 per warp and group");
     // The hardware ties a warp to the TMEM lanes 32 * (warp % 4); four consecutive warps make one column slice.
@@ -316,6 +328,36 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
                 if (n0 + j < shape.n) out[j] += __ldg(bias + n0 + j);
         }
         const size_t element = static_cast<size_t>(row) * shape.ldy + n0;
+        if constexpr (SCATTER) {
+            // The launcher admits only outputs that take whole 32-byte sectors (32-byte aligned copies,
+            // n a multiple of 32, ldy a multiple of a sector).
+            if (shape.y_is_half) {
+                uint32_t packed[COLUMNS / 2];
+#pragma unroll
+                for (int j = 0; j < COLUMNS / 2; ++j) {
+                    const __half2 h = __floats2half2_rn(out[2 * j], out[2 * j + 1]);
+                    packed[j] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                int index = peers.first;
+                for (int copy = 0; copy < peers.count; ++copy) {
+                    __half *target = static_cast<__half *>(peers.y[index]) + element;
+#pragma unroll
+                    for (int j = 0; j < COLUMNS / 16; ++j)
+                        st_global_v8(target + 16 * j, *reinterpret_cast<const uint32_t(*)[8]>(&packed[8 * j]));
+                    if (++index == peers.count) index = 0;
+                }
+            } else {
+                int index = peers.first;
+                for (int copy = 0; copy < peers.count; ++copy) {
+                    float *target = static_cast<float *>(peers.y[index]) + element;
+#pragma unroll
+                    for (int j = 0; j < COLUMNS / 8; ++j)
+                        st_global_v8(target + 8 * j, *reinterpret_cast<const uint32_t(*)[8]>(&out[8 * j]));
+                    if (++index == peers.count) index = 0;
+                }
+            }
+            continue;
+        }
         // whole 32-byte sectors when the row segment is aligned for them, else element by element
         const bool sectors = n0 + COLUMNS <= shape.n &&
                              (reinterpret_cast<uintptr_t>(y) & 31) == 0 && shape.ldy % (shape.y_is_half ? 16 : 8) == 0;
@@ -352,12 +394,12 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
     tmem_load_wait();  // nothing of this warp may still be in flight at teardown
 }
 
-template <bool DUMP_DOTS>
+template <bool DUMP_DOTS, bool SCATTER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
             const __half *__restrict__ a_scales, const __half *__restrict__ w_scales,
             const float *__restrict__ bias, void *__restrict__ y, int32_t *__restrict__ dots_out,
-            const GemmShape shape) {
+            const GemmShape shape, const __grid_constant__ PeerOutputs peers) {
     extern __shared__ uint8_t smem_raw[];
     // the same offsets in both CTAs: the dynamic shared window starts at the same address in each
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -419,7 +461,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
     } else {
         setmaxnreg_inc<FOLD_REGISTERS>();
-        fold_role<DUMP_DOTS>(view, bias, y, dots_out, shape, warp, lane);
+        fold_role<DUMP_DOTS, SCATTER>(view, bias, y, peers, dots_out, shape, warp, lane);
     }
 
     tcgen05_fence_before();

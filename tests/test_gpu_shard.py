@@ -1,4 +1,5 @@
-"""Column-sharded packed linears on 2 GPUs through the C ABI (NCCL all-gather over NVLink).
+"""Column-sharded packed linears on 2 GPUs through the C ABI (NCCL all-gather over NVLink, and the W4A4
+GEMM that stores its slice into every rank's output itself).
 Skipped on a box with fewer than two GPUs."""
 import os
 import socket
@@ -58,6 +59,34 @@ def _worker(rank, ranks, port, result_path):
         assert qi.kernel_status() == 0
         rebuilt = y_slabs.cpu().numpy().transpose(1, 0, 2).reshape(m, n)
         ok = ok and np.array_equal(rebuilt, expected)
+    # scheme 6 without the all-gather: every rank's GEMM stores its slice into every rank's whole output
+    pool = torch.zeros(m * n * (4 + 2), dtype=torch.uint8, device=device)  # one allocation: an fp32 and an fp16 output
+
+    def exchange(item):
+        items = [None] * ranks
+        dist.all_gather_object(items, item)
+        return items
+
+    peers = qi.PeerOutput(context, pool, exchange)
+    a_wide = torch.zeros(m, k, dtype=torch.uint8, device=device)
+    a_scales_device = torch.zeros(m, k // 64, dtype=torch.float16, device=device)
+    assert qi.w4a4_quantize_activations_wide_ex(up(x32), qi.DTYPE_F32, None, a_scales_device, a_wide, m, k, None) == 0
+    shard_wide = torch.zeros(count, k, dtype=torch.uint8, device=device)
+    assert qi.w4a4_widen_codes_ex(up(codes[first:first + count]), shard_wide, count, k) == 0
+    shard_scales = up(scales[first:first + count])
+    for dtype, offset in ((qi.DTYPE_F32, 0), (qi.DTYPE_F16, m * n * 4)):
+        copies = peers.copies(offset)
+        assert qi.w4a4_gemm_wide_scatter_ex(a_wide, a_scales_device, shard_wide, shard_scales, None, copies,
+                                            (rank + 1) % ranks, dtype, n, first, m, count, k, None) == 0
+        assert context.barrier(None) == 0
+    torch.cuda.synchronize()
+    assert qi.kernel_status() == 0
+    whole32 = pool[:m * n * 4].view(torch.float32).view(m, n).cpu().numpy()
+    whole16 = pool[m * n * 4:].view(torch.float16).view(m, n).cpu().numpy()
+    ok = ok and np.array_equal(whole32, expected)
+    ok = ok and np.array_equal(whole16, expected.astype(np.float16))
+    dist.barrier()  # nobody unmaps a copy that another rank may still write
+    peers.close()
     # scheme 5, fp16 output
     codes5, scales5, minimums5 = qt.pack_w4a16(w16)
     record5 = qi.PackedLinear(qi.SCHEME_W4A16, count, k, up(codes5[first:first + count]),
