@@ -277,8 +277,11 @@ def run_b200(args):
     # other ranks map, and the GEMM's epilogue stores its slice into every rank's copy (buffer 0: the device-timed
     # loop; 1 and 2: the end-to-end path's two slots).
     fused = context is not None and args.gather == "fused" and args.w4a4_path == "wide"
+    # "copy": the GEMM writes its slice into this rank's whole output, then the copy engines carry it to the others
+    copied = context is not None and args.gather == "copy" and args.w4a4_path == "wide"
+    placed = fused or copied
     peers = None
-    if fused:
+    if placed:
         sizes = [(m * layer["n"] * 2 + 255) // 256 * 256 for layer in layers]
         pool = torch.empty(3 * sum(sizes), dtype=torch.uint8, device=device)
 
@@ -291,9 +294,10 @@ def run_b200(args):
         offset = 0
         for layer, size in zip(layers, sizes):
             layer["lo"] = qi.shard_plan(layer["n"], world, rank)[0]
-            layer["whole"], layer["copies"] = [], []
+            layer["whole"], layer["copies"], layer["mine"] = [], [], []
             for _ in range(3):
                 layer["whole"].append(pool[offset:offset + m * layer["n"] * 2].view(torch.float16).view(m, layer["n"]))
+                layer["mine"].append(layer["whole"][-1][:, layer["lo"]:layer["lo"] + layer["n_local"]])
                 layer["copies"].append(peers.copies(offset))
                 offset += size
     torch.cuda.synchronize()
@@ -324,6 +328,10 @@ def run_b200(args):
                                                       None, layer["copies"][0 if slot is None else slot + 1],
                                                       (rank + 1) % world, qi.DTYPE_F16, layer["n"], layer["lo"], m,
                                                       n_local, k, stream_handle)
+            elif copied:
+                status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
+                                              None, layer["mine"][0 if slot is None else slot + 1], qi.DTYPE_F16,
+                                              layer["n"], m, n_local, k, stream_handle)
             elif args.w4a4_path == "wide":
                 status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
                                               None, y_out, qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
@@ -343,6 +351,11 @@ def run_b200(args):
                 gather_stream.wait_event(computed_event)
                 if fused:  # the slices are already on their way: what is left is to know that every rank's have landed
                     status = context.barrier(gather_stream.cuda_stream)
+                elif copied:
+                    status = context.put_slice(layer["copies"][0 if slot is None else slot + 1], qi.DTYPE_F16, layer["n"],
+                                               layer["lo"], m, n_local, gather_stream.cuda_stream)
+                    assert status == 0, f"put {layer['name']}: status {status}"
+                    status = context.barrier(gather_stream.cuda_stream)
                 else:
                     status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, gather_stream.cuda_stream)
                 assert status == 0, f"all-gather {layer['name']}: status {status}"
@@ -361,7 +374,7 @@ def run_b200(args):
         step()
     barrier()
     assert qi.kernel_status() == 0, "a kernel gave up on a wait during warm-up"
-    if fused:
+    if placed:
         # every rank's whole outputs, as its peers wrote them, equal what the all-gather of the slices gives
         for layer in layers:
             status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"], None,
@@ -423,8 +436,8 @@ def run_b200(args):
         out_stream.wait_event(computed[slot])
         with torch.cuda.stream(out_stream):
             for layer, hy in zip(layers, host_y):
-                if fused:  # this rank's slice of its whole output
-                    hy.copy_(layer["whole"][slot + 1][:, layer["lo"]:layer["lo"] + layer["n_local"]], non_blocking=True)
+                if placed:  # this rank's slice of its whole output
+                    hy.copy_(layer["mine"][slot + 1], non_blocking=True)
                 else:
                     hy.copy_(layer["y_slots"][slot], non_blocking=True)
         copied_out[slot] = torch.cuda.Event()
@@ -467,7 +480,8 @@ def run_b200(args):
             "data": "synthetic: W ~ N(0,0.02) rotated (H256) and quantised to int4 g64 on the device, "
                     "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
             "config": {"workload": WORKLOAD, "m": m, "ops_per_step": OPS_PER_STEP, "w4a4_path": args.w4a4_path,
-                       "parallelism": "single GPU" if world == 1 else (f"N-sharded x{world}, slices stored to every GPU by the GEMM epilogue + barrier" if fused
+                       "parallelism": "single GPU" if world == 1 else (f"N-sharded x{world}, slices stored to every GPU by the GEMM epilogue + barrier" if fused else
+                                                                              f"N-sharded x{world}, slices put on every GPU by the copy engines + barrier" if copied
                                                                               else f"N-sharded x{world} + NCCL all-gather"),
                        "outputs": "fp16", "l2": f"per-step working set {working_set / 1e6:.0f} MB per GPU exceeds the 126 MB L2"},
             "gpu_launches": timed_launches,
@@ -560,9 +574,10 @@ def main():
     parser.add_argument("--w4a4-path", default="wide", choices=["packed", "wide"],
                         help="packed: the drop-in kernels on nibble-packed codes (int8 tensor-core dots); "
                              "wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
-    parser.add_argument("--gather", default="nccl", choices=["fused", "nccl"],
+    parser.add_argument("--gather", default="nccl", choices=["fused", "copy", "nccl"],
                         help="N > 1: how the column slices reach every GPU. fused: the GEMM's epilogue stores its slice "
-                             "into every GPU's output over NVLink, a barrier follows; nccl: an all-gather after each GEMM")
+                             "into every GPU's output over NVLink, a barrier follows; copy: the copy engines carry the "
+                             "slice to every GPU, a barrier follows; nccl: an all-gather after each GEMM")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

@@ -209,6 +209,14 @@ int qi_w4a4_gemm_wide_scatter_ex(const void *a_bytes, const void *a_scales, cons
                                  const float *bias, void *const *y_copies, int copies, int first_copy, int y_dtype,
                                  long long ldy, int column, int m, int n, int k, void *stream);
 
+/* The same without a kernel of its own: this rank's slice, columns [column, column + n_local) of its
+ * own copy y_copies[rank] (written there by an ordinary GEMM with ldy = N), goes to the same place in
+ * every other copy with one 2-D device-to-device copy per GPU, on the copy engines, so that the SMs
+ * stay with the next GEMM. Ordered on `stream` like a single operation: it starts after the work
+ * queued there before it, and work queued after it starts when all the copies are done. */
+int qi_shard_put_slice(void *context, void *const *y_copies, int copies, int output_dtype, long long ldy, int column,
+                       int rows, int n_local, void *stream);
+
 /* Every rank's work queued on its `stream` before this call has completed when the call's own work
  * completes on any rank's stream (a four-byte NCCL all-reduce). */
 int qi_shard_barrier(void *context, void *stream);

@@ -85,6 +85,7 @@ SIGNATURES = {
     "qi_shard_rank": [_P, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
     "qi_shard_all_gather": [_P, _P, _P, _I, _I, _I, _P],
     "qi_shard_barrier": [_P, _P],
+    "qi_shard_put_slice": [_P, ctypes.POINTER(ctypes.c_void_p), _I, _I, _LL, _I, _I, _I, _P],
     "qi_shard_peer_export": [_P, _P, ctypes.POINTER(ctypes.c_size_t)],
     "qi_shard_peer_open": [_P, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)],
     "qi_shard_peer_close": [_P, ctypes.c_size_t],
@@ -289,6 +290,10 @@ class ShardContext:
 
     def all_gather(self, y_local, y_slabs, output_dtype: int, rows: int, n_local: int, stream=None) -> int:
         return lib().qi_shard_all_gather(self.handle, _p(y_local), _p(y_slabs), output_dtype, rows, n_local, _p(stream))
+
+    def put_slice(self, copies, output_dtype: int, ldy: int, column: int, rows: int, n_local: int, stream=None) -> int:
+        return lib().qi_shard_put_slice(self.handle, copies, len(copies), output_dtype, ldy, column, rows, n_local,
+                                        _p(stream))
 
     def barrier(self, stream=None) -> int:
         return lib().qi_shard_barrier(self.handle, _p(stream))

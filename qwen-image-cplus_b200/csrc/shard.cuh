@@ -62,11 +62,17 @@ inline Nccl &nccl() {
     return api;
 }
 
+constexpr int PUT_LANES = 4;
+
 struct Context {
     uint32_t magic;
     int rank, ranks, device;
     void *comm;
     float *token;  // four bytes for the barrier's all-reduce; allocated by the first barrier
+    // qi_shard_put_slice spreads its copies over these streams, so that several copy engines work at once
+    bool lanes_ready;
+    cudaStream_t lanes[PUT_LANES];
+    cudaEvent_t fork, joins[PUT_LANES];
 };
 
 typedef CUresult (*AddressRange)(CUdeviceptr *, size_t *, CUdeviceptr);
@@ -128,7 +134,8 @@ int qi_shard_create(void **context, int rank, int ranks, const void *id) {
     int device = 0;
     cudaError_t error = cudaGetDevice(&device);
     if (error != cudaSuccess) return static_cast<int>(error);
-    Context *c = new Context{CONTEXT_MAGIC, rank, ranks, device, nullptr, nullptr};
+    Context *c = new Context{};
+    c->magic = CONTEXT_MAGIC, c->rank = rank, c->ranks = ranks, c->device = device;
     UniqueId unique;
     memcpy(&unique, id, sizeof(unique));
     const int result = api.CommInitRank(&c->comm, ranks, unique, rank);
@@ -146,6 +153,13 @@ int qi_shard_destroy(void *context) {
     if (c == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     const int result = c->comm ? nccl().CommDestroy(c->comm) : 0;
     if (c->token != nullptr) cudaFree(c->token);
+    if (c->lanes_ready) {
+        for (int i = 0; i < PUT_LANES; ++i) {
+            cudaStreamDestroy(c->lanes[i]);
+            cudaEventDestroy(c->joins[i]);
+        }
+        cudaEventDestroy(c->fork);
+    }
     c->magic = 0;
     delete c;
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
@@ -187,6 +201,47 @@ int qi_shard_barrier(void *context, void *stream) {
     const int result = nccl().AllReduce(c->token, c->token, 1, NCCL_FLOAT32, 0 /* ncclSum */, c->comm,
                                         static_cast<cudaStream_t>(stream));
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
+int qi_shard_put_slice(void *context, void *const *y_copies, int copies, int output_dtype, long long ldy, int column,
+                       int rows, int n_local, void *stream) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr || y_copies == nullptr || copies != c->ranks || rows <= 0 || n_local <= 0 || column < 0 ||
+        ldy < static_cast<long long>(column) + n_local)
+        return static_cast<int>(cudaErrorInvalidValue);
+    if (output_dtype != QI_DTYPE_F32 && output_dtype != QI_DTYPE_F16) return static_cast<int>(cudaErrorInvalidValue);
+    for (int i = 0; i < copies; ++i)
+        if (y_copies[i] == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    if (copies == 1) return 0;
+    cudaError_t error = cudaSuccess;
+    if (!c->lanes_ready) {
+        for (int i = 0; i < PUT_LANES && error == cudaSuccess; ++i) {
+            error = cudaStreamCreateWithFlags(&c->lanes[i], cudaStreamNonBlocking);
+            if (error == cudaSuccess) error = cudaEventCreateWithFlags(&c->joins[i], cudaEventDisableTiming);
+        }
+        if (error == cudaSuccess) error = cudaEventCreateWithFlags(&c->fork, cudaEventDisableTiming);
+        if (error != cudaSuccess) return static_cast<int>(error);
+        c->lanes_ready = true;
+    }
+    cudaStream_t caller = static_cast<cudaStream_t>(stream);
+    const size_t element = output_dtype == QI_DTYPE_F16 ? 2 : 4;
+    const size_t pitch = static_cast<size_t>(ldy) * element, first_byte = static_cast<size_t>(column) * element;
+    const char *source = static_cast<const char *>(y_copies[c->rank]) + first_byte;
+    const int lanes = copies - 1 < PUT_LANES ? copies - 1 : PUT_LANES;
+    error = cudaEventRecord(c->fork, caller);
+    for (int i = 0; i < lanes && error == cudaSuccess; ++i) error = cudaStreamWaitEvent(c->lanes[i], c->fork, 0);
+    for (int step = 1; step < copies && error == cudaSuccess; ++step) {
+        const int peer = (c->rank + step) % copies;  // every rank starts with another GPU
+        error = cudaMemcpy2DAsync(static_cast<char *>(y_copies[peer]) + first_byte, pitch, source, pitch,
+                                  static_cast<size_t>(n_local) * element, rows, cudaMemcpyDefault,
+                                  c->lanes[(step - 1) % lanes]);
+    }
+    for (int i = 0; i < lanes && error == cudaSuccess; ++i) {
+        error = cudaEventRecord(c->joins[i], c->lanes[i]);
+        if (error == cudaSuccess) error = cudaStreamWaitEvent(caller, c->joins[i], 0);
+    }
+    return static_cast<int>(error);
 }
 
 int qi_shard_peer_export(const void *pointer, void *handle, size_t *offset) {

@@ -85,6 +85,18 @@ def _worker(rank, ranks, port, result_path):
     whole16 = pool[m * n * 4:].view(torch.float16).view(m, n).cpu().numpy()
     ok = ok and np.array_equal(whole32, expected)
     ok = ok and np.array_equal(whole16, expected.astype(np.float16))
+    # the same with the slice written to this rank's own output by the ordinary GEMM and carried to the other by a copy
+    dist.barrier()
+    pool.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    mine = pool[m * n * 4:].view(torch.float16).view(m, n)[:, first:first + count]
+    assert qi.w4a4_gemm_wide_ex(a_wide, a_scales_device, shard_wide, shard_scales, None, mine, qi.DTYPE_F16, n, m, count,
+                                k, None) == 0
+    assert context.put_slice(peers.copies(m * n * 4), qi.DTYPE_F16, n, first, m, count, None) == 0
+    assert context.barrier(None) == 0
+    torch.cuda.synchronize()
+    ok = ok and np.array_equal(pool[m * n * 4:].view(torch.float16).view(m, n).cpu().numpy(), expected.astype(np.float16))
     dist.barrier()  # nobody unmaps a copy that another rank may still write
     peers.close()
     # scheme 5, fp16 output
