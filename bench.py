@@ -276,6 +276,8 @@ def run_b200(args):
     # Without the all-gather: every rank holds every linear's whole output, all of them in ONE allocation that the
     # other ranks map, and the GEMM's epilogue stores its slice into every rank's copy (buffer 0: the device-timed
     # loop; 1 and 2: the end-to-end path's two slots).
+    if args.gather == "auto":
+        args.gather = "copy" if world == 2 and args.w4a4_path == "wide" else "nccl"
     fused = context is not None and args.gather == "fused" and args.w4a4_path == "wide"
     # "copy": the GEMM writes its slice into this rank's whole output, then the copy engines carry it to the others
     copied = context is not None and args.gather == "copy" and args.w4a4_path == "wide"
@@ -574,8 +576,9 @@ def main():
     parser.add_argument("--w4a4-path", default="wide", choices=["packed", "wide"],
                         help="packed: the drop-in kernels on nibble-packed codes (int8 tensor-core dots); "
                              "wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
-    parser.add_argument("--gather", default="nccl", choices=["fused", "copy", "nccl"],
-                        help="N > 1: how the column slices reach every GPU. fused: the GEMM's epilogue stores its slice "
+    parser.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl"],
+                        help="auto: what measured fastest on B200 boxes (copy on 2 GPUs, nccl on 4 and 8). "
+                             "N > 1: how the column slices reach every GPU. fused: the GEMM's epilogue stores its slice "
                              "into every GPU's output over NVLink, a barrier follows; copy: the copy engines carry the "
                              "slice to every GPU, a barrier follows; nccl: an all-gather after each GEMM")
     args = parser.parse_args()
