@@ -280,7 +280,9 @@ def run_b200(args):
         args.gather = "copy" if world == 2 and args.w4a4_path == "wide" else "nccl"
     fused = context is not None and args.gather == "fused" and args.w4a4_path == "wide"
     # "copy": the GEMM writes its slice into this rank's whole output, then the copy engines carry it to the others
-    copied = context is not None and args.gather == "copy" and args.w4a4_path == "wide"
+    # "slabs": the same with the whole output kept as slabs [ranks][rows][N/ranks], so that each copy is one contiguous block
+    slabs = context is not None and args.gather == "slabs" and args.w4a4_path == "wide"
+    copied = slabs or (context is not None and args.gather == "copy" and args.w4a4_path == "wide")
     placed = fused or copied
     peers = None
     if placed:
@@ -298,10 +300,18 @@ def run_b200(args):
             layer["lo"] = qi.shard_plan(layer["n"], world, rank)[0]
             layer["whole"], layer["copies"], layer["mine"] = [], [], []
             for _ in range(3):
-                layer["whole"].append(pool[offset:offset + m * layer["n"] * 2].view(torch.float16).view(m, layer["n"]))
-                layer["mine"].append(layer["whole"][-1][:, layer["lo"]:layer["lo"] + layer["n_local"]])
-                layer["copies"].append(peers.copies(offset))
+                flat = pool[offset:offset + m * layer["n"] * 2].view(torch.float16)
+                if slabs:
+                    layer["whole"].append(flat.view(world, m, layer["n_local"]))
+                    layer["mine"].append(layer["whole"][-1][rank])
+                    layer["copies"].append(peers.copies(offset + rank * m * layer["n_local"] * 2))
+                else:
+                    layer["whole"].append(flat.view(m, layer["n"]))
+                    layer["mine"].append(layer["whole"][-1][:, layer["lo"]:layer["lo"] + layer["n_local"]])
+                    layer["copies"].append(peers.copies(offset))
                 offset += size
+            # rows of the matrix the slice lives in, and the slice's first column there
+            layer["ldy"], layer["column"] = (layer["n_local"], 0) if slabs else (layer["n"], layer["lo"])
     torch.cuda.synchronize()
 
     launches = {"count": 0}
@@ -333,7 +343,7 @@ def run_b200(args):
             elif copied:
                 status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
                                               None, layer["mine"][0 if slot is None else slot + 1], qi.DTYPE_F16,
-                                              layer["n"], m, n_local, k, stream_handle)
+                                              layer["ldy"], m, n_local, k, stream_handle)
             elif args.w4a4_path == "wide":
                 status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"],
                                               None, y_out, qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
@@ -354,8 +364,8 @@ def run_b200(args):
                 if fused:  # the slices are already on their way: what is left is to know that every rank's have landed
                     status = context.barrier(gather_stream.cuda_stream)
                 elif copied:
-                    status = context.put_slice(layer["copies"][0 if slot is None else slot + 1], qi.DTYPE_F16, layer["n"],
-                                               layer["lo"], m, n_local, gather_stream.cuda_stream)
+                    status = context.put_slice(layer["copies"][0 if slot is None else slot + 1], qi.DTYPE_F16, layer["ldy"],
+                                               layer["column"], m, n_local, gather_stream.cuda_stream)
                     assert status == 0, f"put {layer['name']}: status {status}"
                     status = context.barrier(gather_stream.cuda_stream)
                 else:
@@ -385,7 +395,7 @@ def run_b200(args):
             assert status == 0
             assert context.all_gather(layer["y_local"], layer["y_all"], qi.DTYPE_F16, m, layer["n_local"], stream_handle) == 0
             stream.synchronize()
-            gathered = layer["y_all"].permute(1, 0, 2).reshape(m, layer["n"])
+            gathered = layer["y_all"] if slabs else layer["y_all"].permute(1, 0, 2).reshape(m, layer["n"])
             assert torch.equal(gathered, layer["whole"][0]), f"{layer['name']}: the peers' stores differ from the all-gather"
         barrier()
 
@@ -483,7 +493,7 @@ def run_b200(args):
                     "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
             "config": {"workload": WORKLOAD, "m": m, "ops_per_step": OPS_PER_STEP, "w4a4_path": args.w4a4_path,
                        "parallelism": "single GPU" if world == 1 else (f"N-sharded x{world}, slices stored to every GPU by the GEMM epilogue + barrier" if fused else
-                                                                              f"N-sharded x{world}, slices put on every GPU by the copy engines + barrier" if copied
+                                                                              f"N-sharded x{world}, slices put on every GPU by the copy engines ({'slabs' if slabs else 'row-major'}) + barrier" if copied
                                                                               else f"N-sharded x{world} + NCCL all-gather"),
                        "outputs": "fp16", "l2": f"per-step working set {working_set / 1e6:.0f} MB per GPU exceeds the 126 MB L2"},
             "gpu_launches": timed_launches,
@@ -576,11 +586,11 @@ def main():
     parser.add_argument("--w4a4-path", default="wide", choices=["packed", "wide"],
                         help="packed: the drop-in kernels on nibble-packed codes (int8 tensor-core dots); "
                              "wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
-    parser.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl"],
+    parser.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "slabs", "nccl"],
                         help="auto: what measured fastest on B200 boxes (copy on 2 GPUs, nccl on 4 and 8). "
                              "N > 1: how the column slices reach every GPU. fused: the GEMM's epilogue stores its slice "
                              "into every GPU's output over NVLink, a barrier follows; copy: the copy engines carry the "
-                             "slice to every GPU, a barrier follows; nccl: an all-gather after each GEMM")
+                             "slice to every GPU, a barrier follows; slabs: the same with outputs [ranks][rows][N/ranks] (contiguous copies); nccl: an all-gather after each GEMM")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

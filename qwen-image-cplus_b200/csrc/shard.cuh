@@ -233,9 +233,13 @@ int qi_shard_put_slice(void *context, void *const *y_copies, int copies, int out
     for (int i = 0; i < lanes && error == cudaSuccess; ++i) error = cudaStreamWaitEvent(c->lanes[i], c->fork, 0);
     for (int step = 1; step < copies && error == cudaSuccess; ++step) {
         const int peer = (c->rank + step) % copies;  // every rank starts with another GPU
-        error = cudaMemcpy2DAsync(static_cast<char *>(y_copies[peer]) + first_byte, pitch, source, pitch,
-                                  static_cast<size_t>(n_local) * element, rows, cudaMemcpyDefault,
-                                  c->lanes[(step - 1) % lanes]);
+        char *target = static_cast<char *>(y_copies[peer]) + first_byte;
+        const size_t width = static_cast<size_t>(n_local) * element;
+        if (width == pitch)  // the slice is the whole matrix (a slab): one contiguous block
+            error = cudaMemcpyAsync(target, source, width * rows, cudaMemcpyDefault, c->lanes[(step - 1) % lanes]);
+        else
+            error = cudaMemcpy2DAsync(target, pitch, source, pitch, width, rows, cudaMemcpyDefault,
+                                      c->lanes[(step - 1) % lanes]);
     }
     for (int i = 0; i < lanes && error == cudaSuccess; ++i) {
         error = cudaEventRecord(c->joins[i], c->lanes[i]);

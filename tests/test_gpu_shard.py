@@ -97,6 +97,18 @@ def _worker(rank, ranks, port, result_path):
     assert context.barrier(None) == 0
     torch.cuda.synchronize()
     ok = ok and np.array_equal(pool[m * n * 4:].view(torch.float16).view(m, n).cpu().numpy(), expected.astype(np.float16))
+    # and with the whole output kept as slabs [ranks][rows][N/ranks]: the slice is one contiguous block
+    dist.barrier()
+    pool.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    slabs = pool[:ranks * m * count * 4].view(torch.float32).view(ranks, m, count)
+    assert qi.w4a4_gemm_wide_ex(a_wide, a_scales_device, shard_wide, shard_scales, None, slabs[rank], qi.DTYPE_F32, count,
+                                m, count, k, None) == 0
+    assert context.put_slice(peers.copies(rank * m * count * 4), qi.DTYPE_F32, count, 0, m, count, None) == 0
+    assert context.barrier(None) == 0
+    torch.cuda.synchronize()
+    ok = ok and np.array_equal(slabs.cpu().numpy().transpose(1, 0, 2).reshape(m, n), expected)
     dist.barrier()  # nobody unmaps a copy that another rank may still write
     peers.close()
     # scheme 5, fp16 output
