@@ -44,6 +44,36 @@ def test_shard_plan_rejects_illegal_splits(qi):
         qi.shard_plan(0, 1, 0)
 
 
+def test_placing_entry_points_reject_illegal_arguments_before_any_cuda_call(qi):
+    """The argument checks of the entry points that place slices on other GPUs run on the host: they answer
+    cudaErrorInvalidValue (1) without a device."""
+    import ctypes
+    lib = qi.lib()
+    fake = ctypes.c_void_p(0x1000)  # never dereferenced: every call below is rejected by its checks
+    copies = (ctypes.c_void_p * 2)(0x1000, 0x2000)
+    invalid = 1
+    scatter = lib.qi_w4a4_gemm_wide_scatter_ex
+    # no copies, too many copies, a first copy out of range
+    assert scatter(fake, fake, fake, fake, None, None, 2, 0, qi.DTYPE_F16, 512, 0, 128, 256, 256, None) == invalid
+    assert scatter(fake, fake, fake, fake, None, copies, 9, 0, qi.DTYPE_F16, 512, 0, 128, 256, 256, None) == invalid
+    assert scatter(fake, fake, fake, fake, None, copies, 2, 2, qi.DTYPE_F16, 512, 0, 128, 256, 256, None) == invalid
+    # k not a multiple of 256, a column that is not a multiple of 32, a slice that sticks out of the row
+    assert scatter(fake, fake, fake, fake, None, copies, 2, 0, qi.DTYPE_F16, 512, 0, 128, 256, 384, None) == invalid
+    assert scatter(fake, fake, fake, fake, None, copies, 2, 0, qi.DTYPE_F16, 512, 8, 128, 256, 256, None) == invalid
+    assert scatter(fake, fake, fake, fake, None, copies, 2, 0, qi.DTYPE_F16, 256, 32, 128, 256, 256, None) == invalid
+    # a copy that is not aligned for whole 32-byte sectors
+    odd = (ctypes.c_void_p * 2)(0x1000, 0x2010)
+    assert scatter(fake, fake, fake, fake, None, odd, 2, 0, qi.DTYPE_F16, 512, 0, 128, 256, 256, None) == invalid
+    # not a context
+    assert lib.qi_shard_put_slice(None, copies, 2, qi.DTYPE_F16, 512, 0, 128, 256, None) == invalid
+    assert lib.qi_shard_barrier(None, None) == invalid
+    offset = ctypes.c_size_t(0)
+    assert lib.qi_shard_peer_export(None, ctypes.create_string_buffer(64), ctypes.byref(offset)) == invalid
+    pointer = ctypes.c_void_p(0)
+    assert lib.qi_shard_peer_open(None, 0, ctypes.byref(pointer)) == invalid
+    assert lib.qi_shard_peer_close(None, 0) == invalid
+
+
 def slabs_to_row_major(slabs: np.ndarray) -> np.ndarray:
     """[ranks, rows, n_local] -> [rows, ranks * n_local]: column block r is rank r's slice."""
     ranks, rows, n_local = slabs.shape
