@@ -10,8 +10,11 @@
  *     asynchronous errors surface at the caller's next synchronisation;
  *   - all pointers are DEVICE pointers owned by the caller (weights are sub-ranges of one
  *     uploaded pack, so only the pack's 256-byte alignment is assumed; 16 bytes are required);
- *   - nothing is allocated and no state is kept between calls; the device used is the
- *     current one; the un-suffixed entry points launch on the legacy default stream.
+ *   - the operators allocate nothing and keep no state between calls beyond per-device facts
+ *     looked up once (SM count, the kernels' shared-memory opt-in; safe from several host
+ *     threads); the device used is the current one; the un-suffixed entry points launch on the
+ *     legacy default stream. (The sharding context further down owns a communicator, streams
+ *     and events: those are created by qi_shard_create and freed by qi_shard_destroy.)
  *
  * Matrix layouts (row-major):
  *   x        [m, k]     float32 or float16 activations
@@ -88,6 +91,14 @@ int qi_w4a16_gemm_ex(const void *x_half, const void *codes, const void *scales, 
 int qi_w4a16_gemv_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
                      const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
 
+/* As qi_w4a16_gemm_ex with the tile chosen by the caller instead of by shape (for tests and
+ * tuning; every tile gives results within the operator's tolerance, not the same bits):
+ * 0 = by shape, 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256, 5 = 256x256 on a CTA pair.
+ * No counterpart in the reference (gemm.cu:198 has one tile, 128x128x64). */
+int qi_w4a16_gemm_tile_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
+                          const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, int tile,
+                          void *stream);
+
 /* W^[n,k] = fp16(code*scale+minimum) written out as float16 [n,k] (gemm.cu:223-230): the
  * unpacked operand exactly as the GEMM kernels feed it to the tensor cores. */
 int qi_w4a16_dequantize_ex(const void *codes, const void *scales, const void *minimums, void *w_half,
@@ -117,6 +128,13 @@ int qi_w4a4_quantize_activations_wide_ex(const void *x, int x_dtype, void *codes
 /* As qi_w4a4_gemm_ex on byte operands a_bytes [m, k], w_bytes [n, k]; k % 128 == 0. */
 int qi_w4a4_gemm_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                          const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
+
+/* The same operator on one CTA per 128x128 tile instead of a CTA pair per 256x128 tile (the kernel
+ * qi_w4a4_gemm_wide_ex itself falls back to when k is not a multiple of 256 or a scale array is
+ * not 8-byte aligned). `dots` may be NULL; otherwise [m, n, k/64] as below. Same bits. */
+int qi_w4a4_gemm_wide_single_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                                const float *bias, void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n,
+                                int k, void *stream);
 
 /* As qi_w4a4_group_dots_ex, from the byte-operand kernel. */
 int qi_w4a4_group_dots_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
@@ -203,8 +221,15 @@ int qi_shard_peer_close(void *pointer, size_t offset);
  * qi_w4a4_gemm_wide_ex with the output written to `copies` matrices of the same layout, one of
  * them usually this rank's own and the others peer mappings; `column` (a multiple of 32) is where
  * this rank's slice starts, and a CTA stores to copy first_copy first (give each rank another one).
- * k must be a multiple of 256. The stores of a launch are complete when the launch is: a consumer
- * on another rank waits for qi_shard_barrier, placed after the launch in stream order. */
+ * k must be a multiple of 256, n of 32, both scale arrays 8-byte aligned. The stores of a launch
+ * are complete when the launch is: a consumer on another rank waits for qi_shard_barrier, placed
+ * after the launch in stream order.
+ * That barrier orders producers before consumers only. The reverse also needs an order: a copy may
+ * be REWRITTEN (by the next step's launch on any rank) only after every rank's readers of it are
+ * done. Either queue a second qi_shard_barrier after the readers and before the next writer, or
+ * alternate between two sets of copies so that the barrier of step i + 1 (which every rank reaches
+ * only after its readers of step i were queued ahead of it in stream order) guards set i. The same
+ * rule holds for qi_shard_put_slice. */
 int qi_w4a4_gemm_wide_scatter_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                                  const float *bias, void *const *y_copies, int copies, int first_copy, int y_dtype,
                                  long long ldy, int column, int m, int n, int k, void *stream);
@@ -227,12 +252,6 @@ int qi_shard_barrier(void *context, void *stream);
  * (which wait, which stage) and the kernel returns. This reads and clears the code of the
  * current device (0 = healthy). Synchronises the device. */
 int qi_kernel_status(unsigned int *status);
-
-/* Tuning hooks (not for production): force one W4A16 tile shape (1..4, 0 = by shape); switch
- * parts of the GEMM kernels off to see what bounds them (results are then wrong). */
-int qi_tune_w4a16_tile(int tile);
-int qi_tune_ablate(int flags);
-int qi_tune_w4a4_wide_single(int single); /* 1: byte-operand W4A4 on single CTAs instead of CTA pairs */
 
 /* "qipack_b200 <version> sm_100a" */
 const char *qi_b200_version(void);

@@ -94,9 +94,8 @@ SIGNATURES = {
     "qi_shard_linear": [_P, ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _P, _I, _I,
                         _I, _P],
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
-    "qi_tune_w4a16_tile": [_I],
-    "qi_tune_ablate": [_I],
-    "qi_tune_w4a4_wide_single": [_I],
+    "qi_w4a16_gemm_tile_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _P],
+    "qi_w4a4_gemm_wide_single_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _P, _I, _I, _I, _P],
 }
 
 _lib = None
@@ -212,16 +211,18 @@ def kernel_status() -> int:
     return int(value.value)
 
 
-def tune_w4a16_tile(tile: int) -> int:
-    return lib().qi_tune_w4a16_tile(tile)
+def w4a16_gemm_tile_ex(x_half, codes, scales, minimums, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,
+                       tile: int, stream=None) -> int:
+    """qi_w4a16_gemm_ex with the tile forced (1..5; 0 = by shape)."""
+    return lib().qi_w4a16_gemm_tile_ex(_p(x_half), _p(codes), _p(scales), _p(minimums), _p(bias), _p(y), y_dtype,
+                                       ldy, m, n, k, tile, _p(stream))
 
 
-def tune_w4a4_wide_single(single: int) -> int:
-    return lib().qi_tune_w4a4_wide_single(single)
-
-
-def tune_ablate(flags: int) -> int:
-    return lib().qi_tune_ablate(flags)
+def w4a4_gemm_wide_single_ex(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype: int, ldy: int, dots, m: int,
+                             n: int, k: int, stream=None) -> int:
+    """The byte-operand W4A4 GEMM on single CTAs; `dots` [m, n, k/64] int32 or None."""
+    return lib().qi_w4a4_gemm_wide_single_ex(_p(a_bytes), _p(a_scales), _p(w_bytes), _p(w_scales), _p(bias), _p(y),
+                                             y_dtype, ldy, _p(dots), m, n, k, _p(stream))
 
 
 # ---- transformer::linear (transformer.cplus:673-713) ------------------------------------------

@@ -4,6 +4,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -33,15 +34,26 @@ int current_device() {
     return device;
 }
 
+// The lazily filled tables below are atomics: two host threads that meet in a first call both do the
+// (idempotent) query or cudaFuncSetAttribute, and neither reads a half-written entry.
 int sm_count(int device) {
-    static int cached[MAX_DEVICES];
-    if (cached[device] == 0) {
-        int count = 0;
+    static std::atomic<int> cached[MAX_DEVICES];
+    int count = cached[device].load(std::memory_order_relaxed);
+    if (count == 0) {
         if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
             return 148;
-        cached[device] = count;
+        cached[device].store(count, std::memory_order_relaxed);
     }
-    return cached[device];
+    return count;
+}
+
+// Opts a kernel into its dynamic shared memory once per device; `done` is that kernel's per-device flag.
+template <typename Kernel>
+cudaError_t configure_once(Kernel kernel, int smem_bytes, std::atomic<bool> &done) {
+    if (done.load(std::memory_order_acquire)) return cudaSuccess;
+    const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (error == cudaSuccess) done.store(true, std::memory_order_release);
+    return error;
 }
 
 // ---- TMA descriptors ---------------------------------------------------------------------------
@@ -51,13 +63,16 @@ typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, 
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiled encode_tiled() {
-    static EncodeTiled function = nullptr;
+    static std::atomic<EncodeTiled> cached{nullptr};
+    EncodeTiled function = cached.load(std::memory_order_acquire);
     if (function == nullptr) {
         void *entry = nullptr;
         cudaDriverEntryPointQueryResult result;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
+            result == cudaDriverEntryPointSuccess) {
             function = reinterpret_cast<EncodeTiled>(entry);
+            cached.store(function, std::memory_order_release);
+        }
     }
     return function;
 }
@@ -81,10 +96,7 @@ bool make_map(CUtensorMap *map, CUtensorMapDataType type, int element_bytes, con
 
 // ---- tile selection -----------------------------------------------------------------------------
 
-// 0 = choose by shape; otherwise forces one W4A16 tile: 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256,
-// 5 = 256x256 on a pair of CTAs.
-int g_w4a16_tile = 0;
-int g_ablate = 0;  // tuning only, see GemmShape::ablate
+// W4A16 tiles: 0 = choose by shape; 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256, 5 = 256x256 on a pair of CTAs.
 
 template <int NUM_M, int BN, int STAGES>
 int launch_w4a16(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
@@ -98,12 +110,8 @@ int launch_w4a16(const void *x_half, const void *codes, const void *scales, cons
                   static_cast<uint64_t>(shape.k) / 2, 32, BN, CU_TENSOR_MAP_SWIZZLE_NONE))
         return INVALID;
     auto kernel = w4a16::gemm_kernel<NUM_M, BN, STAGES>;
-    static bool configured[MAX_DEVICES];
-    if (!configured[device]) {
-        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-        if (error != cudaSuccess) return static_cast<int>(error);
-        configured[device] = true;
-    }
+    static std::atomic<bool> configured[MAX_DEVICES];
+    if (const cudaError_t error = configure_once(kernel, T::SMEM_BYTES, configured[device])) return static_cast<int>(error);
     const int tiles = ((shape.m + T::BM - 1) / T::BM) * ((shape.n + BN - 1) / BN);
     const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
     kernel<<<grid, w4a16::THREADS, T::SMEM_BYTES, stream>>>(map_x, map_codes, static_cast<const __half *>(scales),
@@ -124,12 +132,8 @@ int launch_w4a16_pair(const void *x_half, const void *codes, const void *scales,
                   static_cast<uint64_t>(shape.k) / 2, 32, wp::BN / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
         return INVALID;
     auto kernel = wp::gemm_kernel<STAGES>;
-    static bool configured[MAX_DEVICES];
-    if (!configured[device]) {
-        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-        if (error != cudaSuccess) return static_cast<int>(error);
-        configured[device] = true;
-    }
+    static std::atomic<bool> configured[MAX_DEVICES];
+    if (const cudaError_t error = configure_once(kernel, T::SMEM_BYTES, configured[device])) return static_cast<int>(error);
     const int tiles = ((shape.m + 2 * wp::BM - 1) / (2 * wp::BM)) * ((shape.n + wp::BN - 1) / wp::BN);
     const int pairs = sm_count(device) / 2;
     const int grid = 2 * (tiles < pairs ? tiles : pairs);  // the kernel carries __cluster_dims__(2, 1, 1)
@@ -150,12 +154,9 @@ int launch_w4a4(const void *a_codes, const void *a_scales, const void *w_codes, 
                   static_cast<uint64_t>(shape.k) / 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_NONE))
         return INVALID;
     auto kernel = dots != nullptr ? w4a4::gemm_kernel<BN, STAGES, true> : w4a4::gemm_kernel<BN, STAGES, false>;
-    static bool configured[MAX_DEVICES][2];
-    if (!configured[device][dots != nullptr]) {
-        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-        if (error != cudaSuccess) return static_cast<int>(error);
-        configured[device][dots != nullptr] = true;
-    }
+    static std::atomic<bool> configured[MAX_DEVICES][2];
+    if (const cudaError_t error = configure_once(kernel, T::SMEM_BYTES, configured[device][dots != nullptr]))
+        return static_cast<int>(error);
     const int tiles = ((shape.m + T::BM - 1) / T::BM) * ((shape.n + BN - 1) / BN);
     const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
     kernel<<<grid, w4a4::THREADS, T::SMEM_BYTES, stream>>>(map_a, map_w, static_cast<const __half *>(a_scales),
@@ -175,21 +176,15 @@ int launch_w4a4_wide(const void *a_bytes, const void *a_scales, const void *w_by
                   w4a4_wide::STAGE_K, w4a4_wide::BN, CU_TENSOR_MAP_SWIZZLE_128B))
         return INVALID;
     auto kernel = dots != nullptr ? w4a4_wide::gemm_kernel<STAGES, true> : w4a4_wide::gemm_kernel<STAGES, false>;
-    static bool configured[MAX_DEVICES][2];
-    if (!configured[device][dots != nullptr]) {
-        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-        if (error != cudaSuccess) return static_cast<int>(error);
-        configured[device][dots != nullptr] = true;
-    }
+    static std::atomic<bool> configured[MAX_DEVICES][2];
+    if (const cudaError_t error = configure_once(kernel, T::SMEM_BYTES, configured[device][dots != nullptr]))
+        return static_cast<int>(error);
     const int tiles = ((shape.m + w4a4_wide::BM - 1) / w4a4_wide::BM) * ((shape.n + w4a4_wide::BN - 1) / w4a4_wide::BN);
     const int grid = tiles < sm_count(device) ? tiles : sm_count(device);
     kernel<<<grid, w4a4_wide::THREADS, T::SMEM_BYTES, stream>>>(map_a, map_w, static_cast<const __half *>(a_scales),
                                                                 static_cast<const __half *>(w_scales), bias, y, dots, shape);
     return static_cast<int>(cudaGetLastError());
 }
-
-// 0 = 256x256 tiles on CTA pairs; 1 = 128x128 tiles on single CTAs (w4a4_wide_gemm.cuh). Tuning hook.
-int g_w4a4_wide_single = 0;
 
 int launch_w4a4_pair(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                      const float *bias, void *y, int32_t *dots, const GemmShape &shape, cudaStream_t stream, int device,
@@ -206,12 +201,9 @@ int launch_w4a4_pair(const void *a_bytes, const void *a_scales, const void *w_by
     const int variant = peers != nullptr ? 2 : (dots != nullptr ? 1 : 0);
     auto kernel = variant == 2 ? wp::gemm_kernel<false, true>
                                : (variant == 1 ? wp::gemm_kernel<true, false> : wp::gemm_kernel<false, false>);
-    static bool configured[MAX_DEVICES][3];
-    if (!configured[device][variant]) {
-        const cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wp::SMEM_BYTES);
-        if (error != cudaSuccess) return static_cast<int>(error);
-        configured[device][variant] = true;
-    }
+    static std::atomic<bool> configured[MAX_DEVICES][3];
+    if (const cudaError_t error = configure_once(kernel, wp::SMEM_BYTES, configured[device][variant]))
+        return static_cast<int>(error);
     const wp::PeerOutputs outputs = peers != nullptr ? *peers : wp::PeerOutputs{};
     const int tiles = ((shape.m + 2 * wp::BM - 1) / (2 * wp::BM)) * ((shape.n + wp::BN - 1) / wp::BN);
     const int pairs = sm_count(device) / 2;
@@ -267,14 +259,13 @@ int w4a16_gemv(const void *x_half, const void *codes, const void *scales, const 
 }
 
 int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
-               void *y, int y_dtype, long long ldy, int m, int n, int k, cudaStream_t stream) {
+               void *y, int y_dtype, long long ldy, int m, int n, int k, int tile, cudaStream_t stream) {
     if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 64 != 0) return INVALID;
     if (!x_half || !codes || !scales || !minimums) return INVALID;
     if (!aligned16(x_half) || !aligned16(codes) || !output_ok(y, y_dtype, ldy, n)) return INVALID;
     const int device = current_device();
     if (device < 0) return INVALID;
-    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
-    int tile = g_w4a16_tile;
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
     if (tile == 0) {
         // Measured on B200 (4096 x {3072, 9216, 12288} x {3072, 12288}, 1024 and 256 rows): per tile the
         // 256x256 tile on one CTA is about 4 % faster than the same tile on a CTA pair, but a pair wave is
@@ -309,13 +300,14 @@ int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, co
         return INVALID;
     const int device = current_device();
     if (device < 0) return INVALID;
-    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
     return launch_w4a4<128, 4>(a_codes, a_scales, w_codes, w_scales, bias, y, dots, shape, stream, device);
 }
 
+// single_cta: always the one-CTA kernel (128 x 128 tiles); otherwise CTA pairs where the shape and pointers allow.
 int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                    const float *bias, void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n, int k,
-                   cudaStream_t stream) {
+                   bool single_cta, cudaStream_t stream) {
     if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 128 != 0) return INVALID;
     if (!a_bytes || !a_scales || !w_bytes || !w_scales) return INVALID;
     if (!aligned16(a_bytes) || !aligned16(w_bytes) || (reinterpret_cast<uintptr_t>(a_scales) & 3) ||
@@ -323,8 +315,11 @@ int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_byte
         return INVALID;
     const int device = current_device();
     if (device < 0) return INVALID;
-    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
-    if (g_w4a4_wide_single || k % w4a4_pair::STAGE_K != 0)  // the pair kernel's stage is four groups
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
+    // The pair kernel's stage is four groups, and it stages both scale arrays eight bytes at a time; anything
+    // else goes to the one-CTA kernel, which takes two groups per stage and four-byte-aligned scales.
+    const bool scales_aligned8 = ((reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(w_scales)) & 7) == 0;
+    if (single_cta || k % w4a4_pair::STAGE_K != 0 || !scales_aligned8)
         return launch_w4a4_wide<6>(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
     return launch_w4a4_pair(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
 }
@@ -373,7 +368,14 @@ int qi_w4a4_widen_codes_ex(const void *codes, void *bytes, long long rows, int k
 
 int qi_w4a4_gemm_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                          const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
-    return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k,
+    return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k, false,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a4_gemm_wide_single_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
+                                const float *bias, void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n,
+                                int k, void *stream) {
+    return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype, ldy, dots, m, n, k, true,
                           static_cast<cudaStream_t>(stream));
 }
 
@@ -385,8 +387,9 @@ int qi_w4a4_gemm_wide_scatter_ex(const void *a_bytes, const void *a_scales, cons
         return INVALID;
     if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % wp::STAGE_K != 0 || column < 0 || column % 32 != 0) return INVALID;
     if (!a_bytes || !a_scales || !w_bytes || !w_scales) return INVALID;
-    if (!aligned16(a_bytes) || !aligned16(w_bytes) || (reinterpret_cast<uintptr_t>(a_scales) & 3) ||
-        (reinterpret_cast<uintptr_t>(w_scales) & 3))
+    // this entry point always runs on CTA pairs, whose scale staging copies eight bytes at a time
+    if (!aligned16(a_bytes) || !aligned16(w_bytes) || (reinterpret_cast<uintptr_t>(a_scales) & 7) ||
+        (reinterpret_cast<uintptr_t>(w_scales) & 7))
         return INVALID;
     if (y_dtype != QI_DTYPE_F16 && y_dtype != QI_DTYPE_F32) return INVALID;
     if (ldy < static_cast<long long>(column) + n) return INVALID;
@@ -402,7 +405,7 @@ int qi_w4a4_gemm_wide_scatter_ex(const void *a_bytes, const void *a_scales, cons
     if ((ldy * static_cast<long long>(element)) % 32 != 0) return INVALID;  // the epilogue stores whole 32-byte sectors
     const int device = current_device();
     if (device < 0) return INVALID;
-    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16, g_ablate};
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
     return launch_w4a4_pair(a_bytes, a_scales, w_bytes, w_scales, bias, outputs.y[first_copy], nullptr, shape,
                             static_cast<cudaStream_t>(stream), device, &outputs);
 }
@@ -410,7 +413,7 @@ int qi_w4a4_gemm_wide_scatter_ex(const void *a_bytes, const void *a_scales, cons
 int qi_w4a4_group_dots_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                                float *y, int32_t *dots, int m, int n, int k, void *stream) {
     if (dots == nullptr) return INVALID;
-    return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, nullptr, y, QI_DTYPE_F32, n, dots, m, n, k,
+    return w4a4_gemm_wide(a_bytes, a_scales, w_bytes, w_scales, nullptr, y, QI_DTYPE_F32, n, dots, m, n, k, false,
                           static_cast<cudaStream_t>(stream));
 }
 
@@ -446,13 +449,20 @@ int qi_w4a16_gemm_ex(const void *x_half, const void *codes, const void *scales, 
                      const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
     if (m >= 1 && m <= 8 && n % 16 == 0)
         return w4a16_gemv(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, static_cast<cudaStream_t>(stream));
-    return w4a16_gemm(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, static_cast<cudaStream_t>(stream));
+    return w4a16_gemm(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, 0, static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a16_gemm_tile_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
+                          const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, int tile,
+                          void *stream) {
+    if (tile < 0 || tile > 5) return INVALID;
+    return w4a16_gemm(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, tile, static_cast<cudaStream_t>(stream));
 }
 
 int qi_w4a16_gemm(const void *x_half, const void *codes, const void *scales, const void *minimums, float *y, int m,
                   int n, int k) {
     if (m % 128 != 0 || n % 128 != 0 || k % 64 != 0) return INVALID;  // gemm.cu:264
-    return w4a16_gemm(x_half, codes, scales, minimums, nullptr, y, QI_DTYPE_F32, n, m, n, k, nullptr);
+    return w4a16_gemm(x_half, codes, scales, minimums, nullptr, y, QI_DTYPE_F32, n, m, n, k, 0, nullptr);
 }
 
 int qi_f32_to_f16(const float *source, void *out, unsigned long long count) {
@@ -531,24 +541,6 @@ int qi_kernel_status(unsigned int *status) {
     }
     *status = value;
     return static_cast<int>(error);
-}
-
-// Forces one W4A16 tile (1..4) or returns to the shape heuristic (0). For tuning runs.
-int qi_tune_w4a16_tile(int tile) {
-    if (tile < 0 || tile > 5) return INVALID;
-    g_w4a16_tile = tile;
-    return 0;
-}
-
-// Tuning only: switches parts of the GEMM kernels off to see what bounds them (results are then wrong).
-int qi_tune_ablate(int flags) {
-    g_ablate = flags;
-    return 0;
-}
-
-int qi_tune_w4a4_wide_single(int single) {
-    g_w4a4_wide_single = single != 0;
-    return 0;
 }
 
 const char *qi_b200_version(void) { return "qipack_b200 0.1 sm_100a"; }

@@ -31,7 +31,6 @@ struct GemmShape {
     int m, n, k;
     long long ldy;    // elements between rows of y
     int y_is_half;    // 0: float32, 1: float16
-    int ablate;       // tuning only: bit 0 skips the unpack/widen math, bit 1 the fold math, bit 2 the y stores
 };
 
 namespace w4a16 {
@@ -205,7 +204,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 uint8_t *b_tile = smem_b + s * T::B_BYTES;
 #pragma unroll
                 for (int p = 0; p < BN / 128; ++p) {
-                    if (shape.ablate & 1) break;
                     const int row = p * 128 + (d >> 1);
                     const uint4 packed = *reinterpret_cast<const uint4 *>(codes_tile + row * 32 + half_row * 16);
                     uint4 out[4];
@@ -237,7 +235,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                     tmem_load_32x32(tmem_row + c * 32, r);
                     tmem_load_wait();
                     const int col = n0 + c * 32;
-                    if (row < shape.m && col < shape.n && !(shape.ablate & 4)) {
+                    if (row < shape.m && col < shape.n) {
                         if (bias != nullptr) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(bias + col + j));

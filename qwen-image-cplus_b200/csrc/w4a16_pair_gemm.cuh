@@ -184,7 +184,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 uint8_t *b_tile = smem_b + s * B_BYTES;
 #pragma unroll
                 for (int p = 0; p < 1; ++p) {
-                    if (shape.ablate & 1) break;
                     const int row = p * 128 + (d >> 1);
                     const uint4 packed = *reinterpret_cast<const uint4 *>(codes_tile + row * 32 + half_row * 16);
                     uint4 out[4];
@@ -215,7 +214,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                     tmem_load_32x32(tmem_row + c * 32, r);
                     tmem_load_wait();
                     const int col = n0 + c * 32;
-                    if (row < shape.m && col < shape.n && !(shape.ablate & 4)) {
+                    if (row < shape.m && col < shape.n) {
                         if (bias != nullptr) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(bias + col + j));

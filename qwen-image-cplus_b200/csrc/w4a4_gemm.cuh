@@ -194,10 +194,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 // 16 bytes (32 nibbles) per task: task -> (row, quarter of the 64-byte packed row)
                 const uint8_t *pa = packed_a + s * T::PACKED_A_BYTES;
                 uint8_t *qa = wide_a + s * T::WIDE_A_BYTES;
-                const bool skip_widen = shape.ablate & 1;
 #pragma unroll
                 for (int i = 0; i < T::BM * 4 / 128; ++i) {
-                    if (skip_widen) break;
                     const int task = i * 128 + t, row = task >> 2, quarter = task & 3;
                     uint4 out[2];
                     widen32(*reinterpret_cast<const uint4 *>(pa + task * 16), out);
@@ -209,7 +207,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 uint8_t *qb = wide_b + s * T::WIDE_B_BYTES;
 #pragma unroll
                 for (int i = 0; i < BN * 4 / 128; ++i) {
-                    if (skip_widen) break;
                     const int task = i * 128 + t, row = task >> 2, quarter = task & 3;
                     uint4 out[2];
                     widen32(*reinterpret_cast<const uint4 *>(pb + task * 16), out);
@@ -271,7 +268,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                     dots_out[(static_cast<size_t>(row) * shape.n + col) * groups + group] = static_cast<int32_t>(r[j]) >> 8;
                             }
                         }
-                        if (shape.ablate & 2) continue;
                         // int32 -> fp32 without the conversion unit (it issues at a quarter of the fp32 rate):
                         // adding the bits of 1.5 * 2^23 to an integer below 2^22 in magnitude gives the float
                         // 1.5 * 2^23 + value exactly; one fp32 subtraction takes the offset away again.
@@ -297,7 +293,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (!alive) break;
             // epilogue straight from the register accumulators
             const int col0 = n0 + column_half * COLUMNS;
-            if (row_inside && !(shape.ablate & 4)) {
+            if (row_inside) {
 #pragma unroll
                 for (int c = 0; c < COLUMNS / 32; ++c) {
                     const int col = col0 + c * 32;

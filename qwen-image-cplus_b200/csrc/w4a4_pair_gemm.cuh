@@ -330,7 +330,9 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
         const size_t element = static_cast<size_t>(row) * shape.ldy + n0;
         if constexpr (SCATTER) {
             // The launcher admits only outputs that take whole 32-byte sectors (32-byte aligned copies,
-            // n a multiple of 32, ldy a multiple of a sector).
+            // n a multiple of 32, ldy a multiple of a sector): a warp's 32 columns lie wholly inside the
+            // matrix or wholly outside it (n not a multiple of the tile's 128 columns).
+            if (n0 >= shape.n) continue;
             if (shape.y_is_half) {
                 uint32_t packed[COLUMNS / 2];
 #pragma unroll

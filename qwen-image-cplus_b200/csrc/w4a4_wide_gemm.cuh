@@ -171,7 +171,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                         tcgen05_fence_after();
 #pragma unroll
                         for (int kk = 0; kk < 2; ++kk)
-                            if (!(shape.ablate & 16)) umma_f8(tmem_base + buffer * BN, umma_desc_k_sw128(a_address + gl * 64 + kk * 32),
+                            umma_f8(tmem_base + buffer * BN, umma_desc_k_sw128(a_address + gl * 64 + kk * 32),
                                     umma_desc_k_sw128(b_address + gl * 64 + kk * 32), idesc, kk);
                         tcgen05_commit(&dot_full[buffer]);
                     }
@@ -250,13 +250,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     if (!mbarrier_wait_warp(&dot_full[buffer], buffer_phase, &g_status, STATUS_WAIT_TMEM_FULL | 0x3000 | buffer, lane)) { alive = false; break; }
                     tcgen05_fence_after();
                     uint32_t r[32];
-                    if (!(shape.ablate & 8)) {
-                        tmem_load_32x32(tmem_base + buffer * BN + slice * COLUMNS + (static_cast<uint32_t>(quadrant * 32) << 16), r);
-                        tmem_load_wait();
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = 0u;
-                    }
+                    tmem_load_32x32(tmem_base + buffer * BN + slice * COLUMNS + (static_cast<uint32_t>(quadrant * 32) << 16), r);
+                    tmem_load_wait();
                     // the dots are in registers: hand the buffer back to the tensor core
                     tcgen05_fence_before();
                     __syncwarp();
@@ -271,7 +266,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                                     static_cast<int32_t>(__uint_as_float(r[j]));
                         }
                     }
-                    if (shape.ablate & 2) continue;
                     const float *sw_group = sw_stage + gl * BN;
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
@@ -289,7 +283,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             if (!alive) break;
             const int col = n0 + slice * COLUMNS;
-            if (row_inside && col < shape.n && !(shape.ablate & 4)) {
+            if (row_inside && col < shape.n) {
                 float v[COLUMNS];
 #pragma unroll
                 for (int j = 0; j < COLUMNS / 2; ++j) unpack_f32x2(acc[j], v[2 * j], v[2 * j + 1]);

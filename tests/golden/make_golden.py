@@ -71,7 +71,8 @@ def pack_nibbles(codes: np.ndarray) -> np.ndarray:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=os.environ.get("QI_REFERENCE"), required="QI_REFERENCE" not in os.environ,
+                        help="path of the netdur/qwen-image-cplus checkout (or set QI_REFERENCE)")
     args = parser.parse_args()
     ref = load_reference(args.reference)
 
