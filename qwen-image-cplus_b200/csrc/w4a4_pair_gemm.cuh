@@ -72,6 +72,11 @@ static_assert(FOLD_WARP0 / 4 * CONTROL_REGISTERS + FOLD_WARPS / 4 * FOLD_REGISTE
 // Pause between polls of the roles that run stages ahead and therefore wait most of the time: a warp that spins
 // takes issue slots from the fold warps of its scheduler.
 constexpr uint32_t AHEAD_BACKOFF_NS = 256;
+// The fold warps and the MMA threads wait for each other group by group. Sixteen warps polling one barrier
+// word with all their lanes slow down every other barrier operation of the CTA, the passing waits of the
+// warps that are behind included (measured: 588 -> 660 TOP/s on the block when the waiting is done by one
+// lane per warp with a pause between polls; a try_wait with a suspend-time hint instead was slower, 572).
+constexpr uint32_t FOLD_BACKOFF_NS = 200, MMA_BACKOFF_NS = 64;
 constexpr int SCALE_AHEAD = 3, SCALE_RING = 4;  // stages of scales in flight; ring slots
 
 constexpr int A_HALF_BYTES = BM * 128, B_HALF_BYTES = (BN / 2) * 128;  // one 128-byte-wide slab of a stage
@@ -229,8 +234,8 @@ __device__ __forceinline__ void mma_role(const View &v, uint32_t mine) {
         const uint32_t iteration = group / STAGE_GROUPS, half = (group % STAGE_GROUPS) >> 1, gl = group & 1;
         const uint32_t s = iteration % STAGES, phase = (iteration / STAGES) & 1;
         const uint32_t buffer = group % BUFFERS, buffer_phase = (group / BUFFERS) & 1;
-        if (!mbarrier_wait(&v.full[s], phase, &g_status, STATUS_WAIT_FULL | 0x5000 | s)) break;
-        if (!mbarrier_wait(&dot_empty[buffer], buffer_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x5000 | buffer)) break;
+        if (!mbarrier_wait(&v.full[s], phase, &g_status, STATUS_WAIT_FULL | 0x5000 | s, MMA_BACKOFF_NS)) break;
+        if (!mbarrier_wait(&dot_empty[buffer], buffer_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x5000 | buffer, MMA_BACKOFF_NS)) break;
         tcgen05_fence_after();
         const uint32_t a_address = smem_u32(v.tile_a + s * A_BYTES + half * A_HALF_BYTES) + gl * 64;
         const uint32_t b_address = smem_u32(v.tile_b + s * B_BYTES + half * B_HALF_BYTES + team * (B_BOX_ROWS * 128)) + gl * 64;
@@ -262,9 +267,8 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
     const uint32_t tmem_lane = v.tmem_base + team * BUFFERS * TEAM_COLUMNS + (slice % (TEAM_COLUMNS / COLUMNS)) * COLUMNS +
                                (static_cast<uint32_t>(quadrant * 32) << 16);
     uint32_t dots[COLUMNS];  // dots[j] = dot of this thread's row and column j of the warp's 32
-    // Waits are per lane (one try_wait when the phase is complete, which it mostly is) and the warp re-converges
-    // at a __syncwarp; a vote on the outcome would add 30 cycles to every group. A lane whose wait ran out of time
-    // sets `failed`; the warp looks at it together once per stage.
+    // A wait starts with one try_wait by every lane (all the warp pays when the phase is complete); only when that
+    // fails does lane 0 poll, with pauses. A wait that ran out of time sets `failed`; the warp looks at it once per stage.
     bool alive = true, failed = false;
     uint32_t iteration = 0, group_count = 0;
     for (int tile = v.pair; tile < v.tiles && alive; tile += v.pairs) {
@@ -277,16 +281,14 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
             const int s = iteration % STAGES;
             const uint32_t phase = (iteration / STAGES) & 1;
             if (__any_sync(0xffffffffu, failed)) { alive = false; break; }
-            failed = !mbarrier_wait(&v.scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x5000 | s);
-            __syncwarp();
+            failed = !mbarrier_wait_warp(&v.scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x5000 | s, lane, FOLD_BACKOFF_NS);
             const float *sw_stage = v.sw_tile + s * STAGE_GROUPS * BN + slice * COLUMNS;
             const float4 sa_quad = v.sa_tile[s * BM + quadrant * 32 + lane];
 #pragma unroll
             for (int gl = 0; gl < STAGE_GROUPS; ++gl, ++group_count) {
                 const uint32_t buffer = group_count % BUFFERS;
-                failed |= !mbarrier_wait(const_cast<uint64_t *>(&dot_full[buffer]), (group_count / BUFFERS) & 1, &g_status,
-                                         STATUS_WAIT_TMEM_FULL | 0x5000 | buffer);
-                __syncwarp();
+                failed |= !mbarrier_wait_warp(const_cast<uint64_t *>(&dot_full[buffer]), (group_count / BUFFERS) & 1, &g_status,
+                                              STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane, FOLD_BACKOFF_NS);
                 tcgen05_fence_after();
                 tmem_load_32x32(tmem_lane + buffer * TEAM_COLUMNS, dots);
                 tmem_load_wait();
