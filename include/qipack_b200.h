@@ -253,6 +253,14 @@ int qi_shard_barrier(void *context, void *stream);
  * current device (0 = healthy). Synchronises the device. */
 int qi_kernel_status(unsigned int *status);
 
+/* What the tensor cores of the current device sustain with nothing in their way: every SM issues dense
+ * tcgen05.mma instructions (128 x 256 x K) on operands resident in shared memory for about `seconds`
+ * (at most 2) and the rate, 2 * multiply-adds per second in units of 1e12, is returned. kind 0: fp16
+ * inputs, fp32 accumulators; 1: FP8 E4M3, fp32; 2: int8, int32. Launches on the legacy default stream
+ * and synchronises. A measuring aid for rooflines: the reference has nothing like it (its
+ * qwen_image_cuda/cuda/bench/bench_gemm_cublas.cu:1-7 times cuBLAS for the same purpose). */
+int qi_probe_tensor_rate(int kind, double seconds, double *tera_ops_per_second);
+
 /* "qipack_b200 <version> sm_100a" */
 const char *qi_b200_version(void);
 

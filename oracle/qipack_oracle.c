@@ -26,10 +26,11 @@ int qio_max_threads(void) {
 #endif
 }
 
+/* An explicit count wins over OMP_NUM_THREADS (launchers such as torch.distributed.run export
+ * OMP_NUM_THREADS=1 to every rank); 0 or less means OpenMP's own default. */
 static int pick_threads(int threads) {
-    int limit = qio_max_threads();
-    if (threads <= 0 || threads > limit) return limit;
-    return threads;
+    if (threads > 0) return threads > 1024 ? 1024 : threads;
+    return qio_max_threads();
 }
 
 /* ---- fp16 (half.cplus:12-79) ---------------------------------------------------- */

@@ -66,7 +66,16 @@ def _c(array, dtype) -> np.ndarray:
 
 
 def max_threads() -> int:
+    """OpenMP's default team size (obeys OMP_NUM_THREADS)."""
     return int(lib().qio_max_threads())
+
+
+def available_cores() -> int:
+    """Host cores this process may run on, whatever OMP_NUM_THREADS says; pass it as `threads=`."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def half_from_f32(value: float) -> int:

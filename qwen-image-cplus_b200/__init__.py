@@ -19,7 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libqipack_b200.so")
 SOURCES = ["qipack_b200.cu", "ptx.cuh", "quantize.cuh", "w4a16_gemm.cuh", "w4a16_gemv.cuh", "w4a16_pair_gemm.cuh", "w4a4_gemm.cuh",
-           "w4a4_wide_gemm.cuh", "w4a4_pair_gemm.cuh", "shard.cuh"]
+           "w4a4_wide_gemm.cuh", "w4a4_pair_gemm.cuh", "shard.cuh", "probe.cuh"]
 
 DTYPE_F32 = 0
 DTYPE_F16 = 1
@@ -94,6 +94,7 @@ SIGNATURES = {
     "qi_shard_linear": [_P, ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _P, _I, _I,
                         _I, _P],
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
+    "qi_probe_tensor_rate": [_I, ctypes.c_double, ctypes.POINTER(ctypes.c_double)],
     "qi_w4a16_gemm_tile_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _P],
     "qi_w4a4_gemm_wide_single_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _P, _I, _I, _I, _P],
 }
@@ -209,6 +210,15 @@ def kernel_status() -> int:
     if error != 0:
         raise RuntimeError(f"qi_kernel_status: cuda status {error}")
     return int(value.value)
+
+
+def probe_tensor_rate(kind: int, seconds: float = 0.05) -> float:
+    """Dense tcgen05.mma rate of the current device in TOP/s; kind 0 fp16, 1 FP8 E4M3, 2 int8."""
+    value = ctypes.c_double(0.0)
+    status = lib().qi_probe_tensor_rate(kind, seconds, ctypes.byref(value))
+    if status != 0:
+        raise RuntimeError(f"qi_probe_tensor_rate: cuda status {status}")
+    return float(value.value)
 
 
 def w4a16_gemm_tile_ex(x_half, codes, scales, minimums, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,

@@ -16,6 +16,7 @@
 #include "w4a4_gemm.cuh"
 #include "w4a4_wide_gemm.cuh"
 #include "w4a4_pair_gemm.cuh"
+#include "probe.cuh"
 
 namespace qi {
 namespace {
@@ -541,6 +542,39 @@ int qi_kernel_status(unsigned int *status) {
     }
     *status = value;
     return static_cast<int>(error);
+}
+
+int qi_probe_tensor_rate(int kind, double seconds, double *tera_ops_per_second) {
+    if (kind < 0 || kind > 2 || !(seconds > 0.0) || seconds > 2.0 || !tera_ops_per_second) return INVALID;
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    void (*kernel)(int) = kind == 0 ? probe::mma_rate_kernel<0> : kind == 1 ? probe::mma_rate_kernel<1> : probe::mma_rate_kernel<2>;
+    cudaError_t error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, probe::SMEM_BYTES);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    const int sms = sm_count(device);
+    const double ops_per_batch = 2.0 * 128 * 256 * (kind == 0 ? 16 : 32) * probe::BATCH * sms;
+    cudaEvent_t begin, end;
+    if ((error = cudaEventCreate(&begin)) != cudaSuccess) return static_cast<int>(error);
+    if ((error = cudaEventCreate(&end)) != cudaSuccess) { cudaEventDestroy(begin); return static_cast<int>(error); }
+    // a short launch sizes the long one: the rate under the power limit differs from the rate of a burst
+    int batches = 64;
+    float ms = 0.0f;
+    for (int round = 0; round < 2 && error == cudaSuccess; ++round) {
+        cudaEventRecord(begin, nullptr);
+        kernel<<<sms, probe::THREADS, probe::SMEM_BYTES>>>(batches);
+        cudaEventRecord(end, nullptr);
+        error = cudaEventSynchronize(end);
+        if (error == cudaSuccess) error = cudaEventElapsedTime(&ms, begin, end);
+        if (round == 0 && error == cudaSuccess && ms > 0.0f) {
+            const double wanted = seconds * 1e3 / ms * batches;
+            batches = wanted > 4e6 ? 4000000 : (wanted < 64 ? 64 : static_cast<int>(wanted));
+        }
+    }
+    cudaEventDestroy(begin);
+    cudaEventDestroy(end);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    *tera_ops_per_second = ops_per_batch * batches / (ms * 1e-3) / 1e12;
+    return 0;
 }
 
 const char *qi_b200_version(void) { return "qipack_b200 0.1 sm_100a"; }
