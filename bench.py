@@ -19,8 +19,9 @@ Workloads (BASELINE.json configs, zero-indexed as the survey reads them):
 
 N > 1 (launched by torch.distributed.run, one rank per GPU): every linear's packed weights are sharded by
 output columns, rank r computes y[:, r*N/R:(r+1)*N/R] and the slices are all-gathered over NVLink; total
-work is fixed (strong scaling). The activation quantiser is sharded by rows and its codes and scales are
-all-gathered (a quarter of the bytes of an fp16 output).
+work is fixed (strong scaling). Every rank quantises all activation rows (--shard-quantiser: its share of
+the rows, the codes and scales all-gathered: a quarter of the bytes of an fp16 output, but two more
+collectives per linear in front of the GEMM).
 
 Prints ONE JSON line. `value` is device-timed with inputs resident in HBM; `e2e` is the same metric through
 the C ABI with host buffers (pinned) copied in and results copied out every step; `roofline` is the W4A4
@@ -402,7 +403,7 @@ def run_block(args):
     assert m % world == 0, "rows must divide by the number of ranks (the quantiser is sharded by rows)"
     generator = torch.Generator(device=device)
     generator.manual_seed(1234)  # same weights and activations on every rank
-    shard_rows = world > 1 and not args.replicate_quantiser
+    shard_rows = world > 1 and args.shard_quantiser
     m_local = m // world if shard_rows else m
     row0 = rank * m_local if shard_rows else 0
     layers, full = [], []
@@ -933,8 +934,10 @@ def main():
                         help="N > 1: how the column slices reach every GPU. nccl (auto): an all-gather after each GEMM; fused: the "
                              "GEMM's epilogue stores its slice into every GPU's output over NVLink, a barrier follows; copy: the copy "
                              "engines carry the slice to every GPU, a barrier follows; slabs: the same with outputs [ranks][rows][N/ranks]")
-    parser.add_argument("--replicate-quantiser", action="store_true",
-                        help="N > 1: every rank quantises all rows instead of its share of them")
+    parser.add_argument("--shard-quantiser", action="store_true",
+                        help="N > 1: every rank quantises its share of the rows and the codes and scales are all-gathered, "
+                             "instead of every rank quantising all rows (measured slower on 2 GPUs: two more NCCL launches "
+                             "per linear in front of the GEMM cost more than the quantiser they save)")
     args = parser.parse_args()
     if args.m is None:
         args.m = 16384 if args.workload == "c4" else 4096
