@@ -261,6 +261,13 @@ int qi_kernel_status(unsigned int *status);
  * qwen_image_cuda/cuda/bench/bench_gemm_cublas.cu:1-7 times cuBLAS for the same purpose). */
 int qi_probe_tensor_rate(int kind, double seconds, double *tera_ops_per_second);
 
+/* Launches one thread that waits, like every wait in this library's kernels, on a barrier that nobody will ever
+ * arrive on, with a time limit of `limit_ns` (at most 1e8) instead of the kernels' two seconds. When the limit
+ * has passed the thread records 0x0001A000 in the status word and the kernel ends; nothing faults or hangs. For
+ * testing what a caller sees after a wait gave up (qi_kernel_status). No counterpart in the reference, whose
+ * kernels have no device-side waits (its error convention: gemm.cu:185-188, transformer.cplus:104-110). */
+int qi_probe_wait_timeout(unsigned long long limit_ns, void *stream);
+
 /* "qipack_b200 <version> sm_100a" */
 const char *qi_b200_version(void);
 

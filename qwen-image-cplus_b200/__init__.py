@@ -95,6 +95,7 @@ SIGNATURES = {
                         _I, _P],
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
     "qi_probe_tensor_rate": [_I, ctypes.c_double, ctypes.POINTER(ctypes.c_double)],
+    "qi_probe_wait_timeout": [_ULL, _P],
     "qi_w4a16_gemm_tile_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _P],
     "qi_w4a4_gemm_wide_single_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _P, _I, _I, _I, _P],
 }
@@ -219,6 +220,11 @@ def probe_tensor_rate(kind: int, seconds: float = 0.05) -> float:
     if status != 0:
         raise RuntimeError(f"qi_probe_tensor_rate: cuda status {status}")
     return float(value.value)
+
+
+def probe_wait_timeout(limit_ns: int, stream=None) -> int:
+    """Launches a wait that runs out after `limit_ns`; kernel_status() then reports 0x0001A000."""
+    return lib().qi_probe_wait_timeout(limit_ns, _p(stream))
 
 
 def w4a16_gemm_tile_ex(x_half, codes, scales, minimums, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,

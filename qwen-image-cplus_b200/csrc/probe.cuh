@@ -62,5 +62,17 @@ __global__ void __launch_bounds__(THREADS, 1) mma_rate_kernel(int batches) {
     }
 }
 
+// A wait that nothing ends: one thread waits on an mbarrier nobody arrives on until `limit_ns` have passed, then
+// does what every wait of this library does when it runs out of time: records the code and returns. Lets a test
+// see the status path (code set, read clears it, the next launch is healthy) without anything going wrong.
+__global__ void __launch_bounds__(32, 1) wait_timeout_kernel(unsigned long long limit_ns) {
+    __shared__ uint64_t never;
+    if (threadIdx.x == 0) {
+        mbarrier_init(&never, 1);
+        fence_barrier_init();
+        mbarrier_wait_spin(&never, 0, &g_status, STATUS_WAIT_FULL | 0xA000, 0, limit_ns);
+    }
+}
+
 }  // namespace probe
 }  // namespace qi

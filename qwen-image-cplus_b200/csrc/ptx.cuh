@@ -89,7 +89,7 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint64_t *barrier, uint32_t pa
 // A wait whose phase is already complete is the common case in a pipeline that runs ahead, and it
 // must cost no more than the one try_wait (about 25 cycles; a loop around it triples that).
 __device__ __forceinline__ bool mbarrier_wait_spin(uint64_t *barrier, uint32_t parity, uint32_t *status, uint32_t code,
-                                                   uint32_t backoff_ns = 0) {
+                                                   uint32_t backoff_ns = 0, uint64_t limit_ns = WAIT_LIMIT_NS) {
     for (uint32_t spin = 0; spin < WAIT_FAST_SPINS; ++spin) {
         if (mbarrier_try_wait(barrier, parity)) return true;
         // A role that runs far ahead of its consumers spends its life here. Without a pause its polling
@@ -102,7 +102,7 @@ __device__ __forceinline__ bool mbarrier_wait_spin(uint64_t *barrier, uint32_t p
         if (mbarrier_try_wait(barrier, parity)) return true;
         __nanosleep(128);
         if (*reinterpret_cast<volatile uint32_t *>(status) != 0) return false;
-        if (global_timer_ns() - start > WAIT_LIMIT_NS) break;
+        if (global_timer_ns() - start > limit_ns) break;
     }
     atomicCAS(status, 0u, code);
     return false;

@@ -577,6 +577,12 @@ int qi_probe_tensor_rate(int kind, double seconds, double *tera_ops_per_second) 
     return 0;
 }
 
+int qi_probe_wait_timeout(unsigned long long limit_ns, void *stream) {
+    if (limit_ns == 0 || limit_ns > 100000000ull) return INVALID;  // at most a tenth of a second
+    probe::wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns);
+    return static_cast<int>(cudaGetLastError());
+}
+
 const char *qi_b200_version(void) { return "qipack_b200 0.1 sm_100a"; }
 
 }  // extern "C"

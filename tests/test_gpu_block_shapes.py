@@ -198,3 +198,90 @@ def test_reference_native_shapes_m1024(qi, reference_kernels, n, k):
         assert reference_kernels.qi_w4a16_gemm(*(ptr(t) for t in args), ptr(y_ref), m, n, k) == 0
         torch.cuda.synchronize()
         assert qt.max_relative_error(y5.cpu().numpy(), y_ref.cpu().numpy()) <= OUTPUT_TOLERANCE
+
+
+# ---- stacks of blocks through the dispatcher: configs 3 and 5 in small -------------------------------------
+
+def run_linear(qi, record, work, x, rows, n):
+    y = torch.full((rows, n), float("nan"), dtype=torch.float16, device="cuda")
+    assert qi.linear(record, work, x, y, rows, input_dtype=qi.DTYPE_F16, output_dtype=qi.DTYPE_F16) == 0
+    check_status(qi)
+    return y.cpu().numpy()
+
+
+def make_work(qi, rows, k_max):
+    return qi.LinearWork(torch.zeros(rows * k_max // 2, dtype=torch.uint8, device="cuda"),
+                         torch.zeros(rows * k_max // 64, dtype=torch.float16, device="cuda"),
+                         torch.zeros(rows * k_max, dtype=torch.float16, device="cuda"),
+                         wide=torch.zeros(rows * k_max, dtype=torch.uint8, device="cuda"))
+
+
+SMALL_BLOCK = [("qkv", 768, 256, "outliers"), ("attn_out", 256, 256, "outliers"), ("fc1", 1024, 256, "outliers"),
+               ("fc2", 256, 1024, "gelu")]  # the block's four linears at hidden 256: every (N, K) relation of the real ones
+
+
+def test_two_blocks_of_the_w4a16_stack_with_text_stream_and_modulation(qi):
+    # config 3 in small: per block the four linears on an image stream and on a text stream with its own weights
+    # (both through qi_linear, scheme 5) and two M = 1 modulation linears (the GEMV path)
+    rng = np.random.default_rng(7300)
+    for block in range(2):
+        for stream_name, rows in (("image", 384), ("text", 40)):
+            work = make_work(qi, rows, 1024)
+            for name, n, k, kind in SMALL_BLOCK:
+                codes, scales, minimums = qt.pack_w4a16(qt.make_weights(rng, n, k))
+                x16 = qt.make_activations(rng, rows, k, kind)
+                record = qi.PackedLinear(qi.SCHEME_W4A16, n, k, up(codes), up(scales), up(minimums))
+                got = run_linear(qi, record, work, up(x16), rows, n)
+                expected = qo.w4a16_gemm(x16, codes, scales, minimums)
+                assert qt.max_relative_error(got.astype(np.float32), expected) <= OUTPUT_TOLERANCE, (block, stream_name, name)
+                distance, checked = qt.fp16_store_error(got, expected)
+                assert distance <= FP16_STORE_ULPS and checked > 0.25, (block, stream_name, name)
+        for _ in range(2):
+            n, k = 6 * 256, 256
+            codes, scales, minimums = qt.pack_w4a16(qt.make_weights(rng, n, k))
+            x16 = qt.make_activations(rng, 1, k, "silu")
+            record = qi.PackedLinear(qi.SCHEME_W4A16, n, k, up(codes), up(scales), up(minimums))
+            got = run_linear(qi, record, make_work(qi, 1, k), up(x16), 1, n)
+            expected = qo.w4a16_gemm(x16, codes, scales, minimums)
+            assert qt.max_relative_error(got.astype(np.float32), expected) <= OUTPUT_TOLERANCE
+
+
+def test_two_blocks_of_the_mixed_policy_stack_with_a_stacked_batch(qi):
+    # config 5 in small: each linear is scheme 6 with probability 0.7, else scheme 5 (seeded, every block draws
+    # both here), and the batch of two is two requests' rows stacked: rows = 2 x (image + text tokens). A row's
+    # result must not depend on what is stacked with it.
+    rng = np.random.default_rng(7500)
+    policy = np.random.default_rng(7501)
+    tokens = 3 * 64 + 24  # three images' tokens and a text stream, per request
+    rows = 2 * tokens
+    work = make_work(qi, rows, 1024)
+    single = make_work(qi, tokens, 1024)
+    schemes_seen = set()
+    for block in range(2):
+        for name, n, k, kind in SMALL_BLOCK:
+            scheme6 = policy.random() < 0.7
+            if block == 1 and name == "fc2" and len(schemes_seen) < 2:
+                scheme6 = qi.SCHEME_W4A4_H256 not in schemes_seen  # make sure both schemes occur
+            w16 = qt.make_weights(rng, n, k)
+            x16 = qt.make_activations(rng, rows, k, kind)
+            if scheme6:
+                schemes_seen.add(qi.SCHEME_W4A4_H256)
+                codes, scales = qt.pack_w4a4(w16)
+                wide = torch.zeros(n, k, dtype=torch.uint8, device="cuda")
+                assert qi.w4a4_widen_codes_ex(up(codes), wide, n, k) == 0
+                record = qi.PackedLinear(qi.SCHEME_W4A4_H256, n, k, up(codes), up(scales), weights_wide=wide)
+                a_codes, a_scales = qo.quantize_activations(x16)
+                expected = qo.w4a4_gemm(a_codes, a_scales, codes, scales)
+            else:
+                schemes_seen.add(qi.SCHEME_W4A16)
+                codes, scales, minimums = qt.pack_w4a16(w16)
+                record = qi.PackedLinear(qi.SCHEME_W4A16, n, k, up(codes), up(scales), up(minimums))
+                expected = qo.w4a16_gemm(x16, codes, scales, minimums)
+            got = run_linear(qi, record, work, up(x16), rows, n)
+            assert qt.max_relative_error(got.astype(np.float32), expected) <= OUTPUT_TOLERANCE, (block, name, scheme6)
+            distance, checked = qt.fp16_store_error(got, expected)
+            assert distance <= FP16_STORE_ULPS and checked > 0.25, (block, name, scheme6)
+            if scheme6:  # exact operator: the stacked batch gives each request the bits it gets alone
+                alone = run_linear(qi, record, single, up(x16[tokens:]), tokens, n)
+                assert np.array_equal(alone, got[tokens:]), (block, name)
+    assert schemes_seen == {qi.SCHEME_W4A4_H256, qi.SCHEME_W4A16}

@@ -528,3 +528,27 @@ def test_linear_takes_the_wide_path_when_given_wide_operands(qi):
     a_codes, a_scales = qo.quantize_activations(x32)
     assert np.array_equal(y.cpu().numpy(), qo.w4a4_gemm(a_codes, a_scales, codes, scales))
     assert work.wide.abs().sum().item() > 0  # the byte arena was really used
+
+
+# ---- a wait that runs out ------------------------------------------------------------------------------
+
+def test_a_wait_that_runs_out_reports_its_code_and_leaves_the_device_healthy(qi):
+    # every device-side wait of the library is bounded; this makes one run out on purpose (a barrier nothing
+    # arrives on, limit 1 ms) and follows the error path a caller would see: code set, cleared by reading it,
+    # and the next launches unaffected
+    assert qi.kernel_status() == 0
+    assert qi.probe_wait_timeout(1_000_000) == 0
+    torch.cuda.synchronize()
+    code = qi.kernel_status()
+    assert code == 0x0001A000, hex(code)
+    assert qi.kernel_status() == 0  # reading clears it
+    assert qi.probe_wait_timeout(0) == qi.CUDA_ERROR_INVALID_VALUE
+    assert qi.probe_wait_timeout(10**9) == qi.CUDA_ERROR_INVALID_VALUE
+    rng = np.random.default_rng(808)
+    m, n, k = 256, 256, 512
+    w_codes, w_scales = qt.random_w4a4_pack(rng, n, k, 1e-3, 6e-3)
+    a_codes, a_scales = qt.random_w4a4_pack(rng, m, k, 0.05, 0.6)
+    y = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    assert qi.w4a4_gemm(up(a_codes), up(a_scales), up(w_codes), up(w_scales), y, m, n, k) == 0
+    check_status(qi)
+    assert np.array_equal(y.cpu().numpy(), qo.w4a4_gemm(a_codes, a_scales, w_codes, w_scales))
