@@ -172,6 +172,82 @@ typedef struct qi_linear_work {
 int qi_linear(const qi_packed_linear *record, const qi_linear_work *work, const void *input, int input_dtype,
               void *output, int output_dtype, long long ld_output, int rows, int reuse_input, void *stream);
 
+/* ---- the QIPACK v6 container (host side) ---------------------------------------------------- */
+/* A pack is a 256-byte header, a directory of 256-byte records, key=value metadata lines in the padding
+ * after the directory, and a data section of 256-byte-aligned regions whose bytes are uploaded verbatim
+ * and addressed by file offset (int4_pack.cplus:36-95, 476-518; transformer.cplus:120-123, 569-572).
+ * These functions read, check and write that container; they run on the host and touch no GPU.
+ * They return 0 or one of the QI_PACK_* codes. Quantising weights is the offline packer's job
+ * (qwen-image-quantize, qwen_image_quantize/src/main.cplus:15-55) and is not repeated here. */
+
+#define QI_PACK_IO 20001               /* cannot open, read, write or rename */
+#define QI_PACK_NOT_A_PACK 20002       /* magic, header size or tensor count */
+#define QI_PACK_POLICY 20003           /* not one of transformer:w4a16-g{32,64,128}-v6, transformer:w4a4-h256-g{..}-v6 */
+#define QI_PACK_METADATA 20004         /* metadata outside the directory padding, checksum mismatch, or key not found */
+#define QI_PACK_RECORD 20005           /* a record's sizes do not follow from its dimensions, or an unknown scheme */
+#define QI_PACK_LAYOUT 20006           /* a region is misaligned, overlaps an earlier one or leaves the file */
+#define QI_PACK_TENSOR_CHECKSUM 20007
+#define QI_PACK_INVENTORY 20008        /* wrong number of quantised matrices, or bytes after the last region */
+#define QI_PACK_PAYLOAD_CHECKSUM 20009
+#define QI_PACK_ARGUMENT 20010
+
+typedef struct qi_pack_header_info {
+    char policy[33];          /* e.g. "transformer:w4a4-h256-g64-v6" (int4_pack.cplus:107-112) */
+    uint32_t scheme;          /* the quantised scheme the policy announces, 0 if none */
+    uint32_t tensor_count;
+    uint64_t data_offset;     /* file offset of the data section: device address = base + (offset - data_offset) */
+    uint64_t file_bytes;
+    uint64_t payload_checksum;
+} qi_pack_header_info;
+
+typedef struct qi_pack_record_info {  /* int4_pack.cplus:76-95 */
+    char name[129];
+    uint32_t scheme, rank;
+    uint64_t dimensions[4];   /* [0] = outputs n, [1] = inputs k for a matrix */
+    uint32_t group_size;
+    uint64_t weights_offset, weights_length, scales_offset, scales_length, zeros_offset, zeros_length;
+    uint64_t tensor_checksum; /* FNV-1a over weights, scales, zeros in that order */
+} qi_pack_record_info;
+
+/* Opens a pack and reads its header, directory and metadata (replaces the reading half of
+ * int4_pack.cplus:220-235 and pack_info.cplus:62-145). */
+int qi_pack_open(const char *path, void **pack);
+int qi_pack_close(void *pack);
+int qi_pack_info(void *pack, qi_pack_header_info *info);
+int qi_pack_record(void *pack, int index, qi_pack_record_info *info);
+/* The value of a metadata line `key=value` (steps, kind, schedule, cache, quant ...: pack_info.cplus:1-5). */
+int qi_pack_metadata(void *pack, const char *key, char *value, size_t capacity);
+/* `bytes` bytes of the file from `offset` into host memory `out` (for the caller's upload of the data section). */
+int qi_pack_read(void *pack, uint64_t offset, uint64_t bytes, void *out);
+/* Record `index` as the run-time view the kernels take, for a data section resident at device address
+ * `device_data` (what transformer.cplus:569-572 computes per call); QI_PACK_RECORD unless it is a scheme 5 or 6 matrix. */
+int qi_pack_linear(void *pack, int index, const void *device_data, struct qi_packed_linear *linear);
+
+/* Everything the reference's verify re-checks (int4_pack.cplus:733-850): policy, metadata placement and checksum,
+ * every record's sizes, alignment and order of the regions, every tensor checksum, the inventory and the payload
+ * checksum. qi_pack_verify expects the engine's 297 tensors of which 224 quantised matrices, as the reference
+ * does; qi_pack_verify_ex takes the expected counts (negative = any). */
+int qi_pack_verify(const char *path);
+int qi_pack_verify_ex(const char *path, int expected_tensors, int expected_matrices);
+
+/* One tensor in its stored form, for qi_pack_write. A matrix of the pack's quantised scheme carries codes
+ * [n, k/2], scales [n, k/group] fp16 and, for scheme 5, zeros (minimums) likewise; anything else is scheme 0
+ * (bf16) or 1 (fp16) raw bytes in `weights`. */
+typedef struct qi_pack_tensor {
+    const char *name;
+    uint32_t scheme, rank;
+    uint64_t dimensions[4];
+    uint32_t group_size;
+    const void *weights; uint64_t weights_length;
+    const void *scales; uint64_t scales_length;
+    const void *zeros; uint64_t zeros_length;
+} qi_pack_tensor;
+
+/* Writes a pack: regions laid out as plan_record does (int4_pack.cplus:476-518), checksums as write_from
+ * computes them (:628-666), to <path>.tmp, verified, then renamed over `path` (:667-677). `metadata`: the
+ * key=value lines, each ending in a newline, or NULL. */
+int qi_pack_write(const char *path, const char *policy, const char *metadata, const qi_pack_tensor *tensors, int count);
+
 /* ---- column (N) sharding over the GPUs of one box ------------------------------------------- */
 /* No counterpart in the reference, which drives one GPU (qwen_image_cuda/cuda/runtime.cu:6-19).
  * One process per GPU. Rank r of R holds weight rows [r*N/R, (r+1)*N/R) of every region (codes,

@@ -19,7 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libqipack_b200.so")
 SOURCES = ["qipack_b200.cu", "ptx.cuh", "quantize.cuh", "w4a16_gemm.cuh", "w4a16_gemv.cuh", "w4a16_pair_gemm.cuh", "w4a4_gemm.cuh",
-           "w4a4_wide_gemm.cuh", "w4a4_pair_gemm.cuh", "shard.cuh", "probe.cuh"]
+           "w4a4_wide_gemm.cuh", "w4a4_pair_gemm.cuh", "shard.cuh", "probe.cuh", "pack_file.cuh"]
 
 DTYPE_F32 = 0
 DTYPE_F16 = 1
@@ -59,6 +59,27 @@ class qi_linear_work(ctypes.Structure):
                 ("wide", ctypes.c_void_p)]
 
 
+class qi_pack_header_info(ctypes.Structure):
+    _fields_ = [("policy", ctypes.c_char * 33), ("scheme", ctypes.c_uint32), ("tensor_count", ctypes.c_uint32),
+                ("data_offset", ctypes.c_uint64), ("file_bytes", ctypes.c_uint64), ("payload_checksum", ctypes.c_uint64)]
+
+
+class qi_pack_record_info(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 129), ("scheme", ctypes.c_uint32), ("rank", ctypes.c_uint32),
+                ("dimensions", ctypes.c_uint64 * 4), ("group_size", ctypes.c_uint32),
+                ("weights_offset", ctypes.c_uint64), ("weights_length", ctypes.c_uint64),
+                ("scales_offset", ctypes.c_uint64), ("scales_length", ctypes.c_uint64),
+                ("zeros_offset", ctypes.c_uint64), ("zeros_length", ctypes.c_uint64), ("tensor_checksum", ctypes.c_uint64)]
+
+
+class qi_pack_tensor(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char_p), ("scheme", ctypes.c_uint32), ("rank", ctypes.c_uint32),
+                ("dimensions", ctypes.c_uint64 * 4), ("group_size", ctypes.c_uint32),
+                ("weights", ctypes.c_void_p), ("weights_length", ctypes.c_uint64),
+                ("scales", ctypes.c_void_p), ("scales_length", ctypes.c_uint64),
+                ("zeros", ctypes.c_void_p), ("zeros_length", ctypes.c_uint64)]
+
+
 _P, _I, _LL, _ULL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_ulonglong
 
 # name -> argument types; every entry point of include/qipack_b200.h
@@ -93,6 +114,16 @@ SIGNATURES = {
                                      _I, _P],
     "qi_shard_linear": [_P, ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _P, _I, _I,
                         _I, _P],
+    "qi_pack_open": [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)],
+    "qi_pack_close": [_P],
+    "qi_pack_info": [_P, ctypes.POINTER(qi_pack_header_info)],
+    "qi_pack_record": [_P, _I, ctypes.POINTER(qi_pack_record_info)],
+    "qi_pack_metadata": [_P, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t],
+    "qi_pack_read": [_P, ctypes.c_uint64, ctypes.c_uint64, _P],
+    "qi_pack_linear": [_P, _I, _P, ctypes.POINTER(qi_packed_linear)],
+    "qi_pack_verify": [ctypes.c_char_p],
+    "qi_pack_verify_ex": [ctypes.c_char_p, _I, _I],
+    "qi_pack_write": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(qi_pack_tensor), _I],
     "qi_kernel_status": [ctypes.POINTER(ctypes.c_uint)],
     "qi_probe_tensor_rate": [_I, ctypes.c_double, ctypes.POINTER(ctypes.c_double)],
     "qi_probe_wait_timeout": [_ULL, _P],
@@ -270,6 +301,102 @@ def linear(model: PackedLinear, work: LinearWork, input, output, rows: int, reus
     return lib().qi_linear(ctypes.byref(model.record), ctypes.byref(work.work), _p(input), input_dtype, _p(output),
                            output_dtype, model.n if ld_output is None else ld_output, rows, int(reuse_input),
                            _p(stream))
+
+
+# ---- the QIPACK v6 container (host side; int4_pack.cplus:36-95, 476-518, 733-850) ------------------------
+
+class PackError(RuntimeError):
+    def __init__(self, what: str, code: int):
+        super().__init__(f"{what}: pack status {code}")
+        self.code = code
+
+
+def pack_write(path: str, policy: str, tensors, metadata: str = "") -> None:
+    """Writes a pack. `tensors`: dicts with name, scheme, dimensions and the stored bytes as NumPy arrays:
+    weights, and for a quantised matrix scales (and zeros for scheme 5) plus group_size."""
+    import numpy as np
+
+    keep, items = [], (qi_pack_tensor * len(tensors))()
+    for item, tensor in zip(items, tensors):
+        item.name = tensor["name"].encode()
+        item.scheme, item.rank = tensor["scheme"], len(tensor["dimensions"])
+        for index, size in enumerate(tensor["dimensions"]):
+            item.dimensions[index] = size
+        item.group_size = tensor.get("group_size", 0)
+        for field in ("weights", "scales", "zeros"):
+            array = tensor.get(field)
+            if array is not None:
+                array = np.ascontiguousarray(array)
+                keep.append(array)
+                setattr(item, field, array.ctypes.data)
+                setattr(item, field + "_length", array.nbytes)
+    status = lib().qi_pack_write(path.encode(), policy.encode(), metadata.encode(), items, len(tensors))
+    if status != 0:
+        raise PackError(f"qi_pack_write({path})", status)
+
+
+def pack_verify(path: str, expected_tensors: int | None = None, expected_matrices: int | None = None) -> int:
+    """0 when the pack passes every check of the reference's verify; with no counts given, the engine's own
+    inventory (297 tensors, 224 quantised matrices) is expected."""
+    if expected_tensors is None and expected_matrices is None:
+        return lib().qi_pack_verify(path.encode())
+    return lib().qi_pack_verify_ex(path.encode(), -1 if expected_tensors is None else expected_tensors,
+                                   -1 if expected_matrices is None else expected_matrices)
+
+
+class Pack:
+    """An open pack: header, records, metadata; `linear(index, device_data)` gives the kernels' view of a record."""
+
+    def __init__(self, path: str):
+        self.handle = ctypes.c_void_p(0)
+        status = lib().qi_pack_open(path.encode(), ctypes.byref(self.handle))
+        if status != 0:
+            raise PackError(f"qi_pack_open({path})", status)
+        info = qi_pack_header_info()
+        lib().qi_pack_info(self.handle, ctypes.byref(info))
+        self.policy, self.scheme, self.tensor_count = info.policy.decode(), info.scheme, info.tensor_count
+        self.data_offset, self.file_bytes, self.payload_checksum = info.data_offset, info.file_bytes, info.payload_checksum
+
+    def record(self, index: int) -> qi_pack_record_info:
+        info = qi_pack_record_info()
+        status = lib().qi_pack_record(self.handle, index, ctypes.byref(info))
+        if status != 0:
+            raise PackError(f"qi_pack_record({index})", status)
+        return info
+
+    def metadata(self, key: str):
+        value = ctypes.create_string_buffer(256)
+        status = lib().qi_pack_metadata(self.handle, key.encode(), value, 256)
+        return value.value.decode() if status == 0 else None
+
+    def read(self, offset: int, count: int):
+        import numpy as np
+
+        out = np.empty(count, dtype=np.uint8)
+        status = lib().qi_pack_read(self.handle, offset, count, out.ctypes.data)
+        if status != 0:
+            raise PackError(f"qi_pack_read({offset}, {count})", status)
+        return out
+
+    def data(self):
+        """The whole data section, as the engine uploads it (transformer.cplus:120-123)."""
+        return self.read(self.data_offset, self.file_bytes - self.data_offset)
+
+    def linear(self, index: int, device_data) -> "PackedLinear":
+        record = qi_packed_linear()
+        status = lib().qi_pack_linear(self.handle, index, _p(device_data), ctypes.byref(record))
+        if status != 0:
+            raise PackError(f"qi_pack_linear({index})", status)
+        view = PackedLinear.__new__(PackedLinear)
+        view.scheme, view.n, view.k, view.group_size = record.scheme, record.n, record.k, record.group_size
+        view.weights = view.scales = view.zeros = view.bias = view.weights_wide = device_data  # keeps the upload alive
+        view.record = record
+        return view
+
+    def close(self) -> None:
+        if self.handle:
+            lib().qi_pack_close(self.handle)
+            self.handle = ctypes.c_void_p(0)
 
 
 # ---- column sharding over the GPUs of one box ------------------------------------------------------

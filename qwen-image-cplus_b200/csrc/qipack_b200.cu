@@ -588,3 +588,4 @@ const char *qi_b200_version(void) { return "qipack_b200 0.1 sm_100a"; }
 }  // extern "C"
 
 #include "shard.cuh"
+#include "pack_file.cuh"
