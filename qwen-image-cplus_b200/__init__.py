@@ -18,7 +18,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libqipack_b200.so")
-SOURCES = ["qipack_b200.cu", "ptx.cuh", "quantize.cuh", "w4a16_gemm.cuh", "w4a16_gemv.cuh", "w4a16_pair_gemm.cuh", "w4a4_gemm.cuh",
+SOURCES = ["qipack_b200.cu", "ptx.cuh", "quantize.cuh", "w4a16_gemm.cuh", "w4a16_gemv.cuh", "w4a16_gemv_stream.cuh", "w4a16_pair_gemm.cuh", "w4a4_gemm.cuh",
            "w4a4_wide_gemm.cuh", "w4a4_pair_gemm.cuh", "shard.cuh", "probe.cuh", "pack_file.cuh"]
 
 DTYPE_F32 = 0

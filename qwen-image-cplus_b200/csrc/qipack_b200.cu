@@ -12,6 +12,7 @@
 #include "quantize.cuh"
 #include "w4a16_gemm.cuh"
 #include "w4a16_gemv.cuh"
+#include "w4a16_gemv_stream.cuh"
 #include "w4a16_pair_gemm.cuh"
 #include "w4a4_gemm.cuh"
 #include "w4a4_wide_gemm.cuh"
@@ -247,6 +248,26 @@ int w4a16_gemv(const void *x_half, const void *codes, const void *scales, const 
     if (!x_half || !codes || !scales || !minimums || !y) return INVALID;
     if (!aligned16(x_half) || !aligned16(codes) || (k % 8) != 0) return INVALID;
     if (ldy < n || (y_dtype != QI_DTYPE_F32 && y_dtype != QI_DTYPE_F16)) return INVALID;
+    // Rows short enough for 16 of them to fit a stage, and regions that bulk copies can take: the streaming kernel.
+    if (k <= w4a16::STREAM_MAX_K && aligned16(scales) && aligned16(minimums)) {
+        const int device = current_device();
+        if (device < 0) return INVALID;
+        // two CTAs per SM: as many stages (at most three) as fit 110 KB beside the activations
+        constexpr int CTA_BYTES = 110 * 1024;
+        int stages = (CTA_BYTES - 128 - w4a16::stream_x_bytes(m, k)) / w4a16::stream_stage_bytes(k);
+        stages = stages > w4a16::STREAM_MAX_STAGES ? w4a16::STREAM_MAX_STAGES : stages;
+        static std::atomic<bool> configured[MAX_DEVICES];
+        if (const cudaError_t error = configure_once(w4a16::gemv_stream_kernel, CTA_BYTES, configured[device]))
+            return static_cast<int>(error);
+        if (stages >= 1) {
+            const int smem_bytes = stages * w4a16::stream_stage_bytes(k) + w4a16::stream_x_bytes(m, k) + 128;
+            const int tiles = n / w4a16::STREAM_ROWS, resident = 2 * sm_count(device);
+            w4a16::gemv_stream_kernel<<<tiles < resident ? tiles : resident, w4a16::STREAM_THREADS, smem_bytes, stream>>>(
+                static_cast<const __half *>(x_half), static_cast<const uint8_t *>(codes), static_cast<const __half *>(scales),
+                static_cast<const __half *>(minimums), bias, y, m, n, k, ldy, y_dtype == QI_DTYPE_F16, stages);
+            return static_cast<int>(cudaGetLastError());
+        }
+    }
     const int quads = (k / 64 + 3) / 4;
     int k_splits = 1;
     for (int candidate = 8; candidate >= 1; candidate /= 2)
