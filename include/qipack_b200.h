@@ -125,6 +125,17 @@ int qi_w4a4_widen_codes_ex(const void *codes, void *bytes, long long rows, int k
 int qi_w4a4_quantize_activations_wide_ex(const void *x, int x_dtype, void *codes, void *scales, void *bytes, int m,
                                          int k, void *stream);
 
+/* The activation function that feeds a scheme-6 linear, fused into its quantiser: the same codes, scales and
+ * bytes as running the reference's element-wise kernel into an [m, k] float32 matrix and quantising that
+ * (the producer's expression is evaluated as the reference writes it), without that matrix in HBM.
+ *   qi_w4a4_swiglu_quantize_ex: silu(gate) * up, i.e. qi_swiglu (qwen_image_cuda/cuda/ops.cu:133-145), the
+ *     input of the down projection (transformer.cplus:811-813), then qi_w4a4_quantize_activations (gemm.cu:22-57);
+ *   qi_w4a4_gelu_quantize_ex: qi_gelu_tanh (ops.cu:155-166), the fc2 input of an MMDiT block, then the same.
+ * gate, up, x: [m, k] float32. codes [m, k/2] and bytes [m, k] may each be NULL, not both; scales [m, k/64]. */
+int qi_w4a4_swiglu_quantize_ex(const float *gate, const float *up, void *codes, void *scales, void *bytes, int m, int k,
+                               void *stream);
+int qi_w4a4_gelu_quantize_ex(const float *x, void *codes, void *scales, void *bytes, int m, int k, void *stream);
+
 /* As qi_w4a4_gemm_ex on byte operands a_bytes [m, k], w_bytes [n, k]; k % 128 == 0. */
 int qi_w4a4_gemm_wide_ex(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                          const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
@@ -278,6 +289,19 @@ int qi_shard_all_gather(void *context, const void *y_local, void *y_slabs, int o
 int qi_shard_linear(void *context, const qi_packed_linear *local_record, const qi_linear_work *work,
                     const void *input, int input_dtype, void *y_local, void *y_slabs, int output_dtype, int rows,
                     int reuse_input, void *stream);
+
+/* The other split (row-parallel): rank r holds input columns [r*K/R, (r+1)*K/R) of every weight row - a column block
+ * of codes [n, K/R/2], scales and minimums [n, K/R/64], copied out of the pack by the caller - and the matching
+ * columns of the activations, computes the partial product over its inputs in float32 and the partial results are
+ * summed over the ranks (ncclAllReduce, in place): every rank ends with the whole y [rows, n]. It pairs with a
+ * column-sharded linear in front of it (fc1 -> activation -> fc2: the column slice a rank computed is the input
+ * slice it needs), so that the wide tensor between them is never gathered. K/R must hold whole groups, and for
+ * scheme 6 whole 256-input Hadamard blocks; then the slice's activation codes are the unsharded codes' slice. The
+ * sum over ranks is a float32 sum in NCCL's order: the result agrees with the unsharded operator to float32
+ * rounding of R partial sums, not bit for bit. A bias may be given on rank 0 only. */
+int qi_shard_plan_inputs(int k, int scheme, int ranks, int rank, int *first_input, int *input_count);
+int qi_shard_linear_inputs(void *context, const struct qi_packed_linear *local_record, const struct qi_linear_work *work,
+                           const void *input_local, int input_dtype, float *y, int rows, int reuse_input, void *stream);
 
 /* The W4A4 linear without the all-gather: every rank holds the whole output y [rows, N] and the
  * GEMM stores its slice into every rank's copy itself, over NVLink, from its epilogue.

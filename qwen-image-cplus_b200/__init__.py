@@ -97,9 +97,13 @@ SIGNATURES = {
     "qi_w4a4_widen_codes_ex": [_P, _P, _LL, _I, _P],
     "qi_w4a4_quantize_activations_wide_ex": [_P, _I, _P, _P, _P, _I, _I, _P],
     "qi_w4a4_gemm_wide_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
+    "qi_w4a4_swiglu_quantize_ex": [_P, _P, _P, _P, _P, _I, _I, _P],
+    "qi_w4a4_gelu_quantize_ex": [_P, _P, _P, _P, _I, _I, _P],
     "qi_w4a4_group_dots_wide_ex": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "qi_linear": [ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _I, _LL, _I, _I, _P],
     "qi_shard_plan": [_I, _I, _I, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+    "qi_shard_plan_inputs": [_I, _I, _I, _I, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+    "qi_shard_linear_inputs": [_P, ctypes.POINTER(qi_packed_linear), ctypes.POINTER(qi_linear_work), _P, _I, _P, _I, _I, _P],
     "qi_shard_unique_id": [_P],
     "qi_shard_create": [ctypes.POINTER(ctypes.c_void_p), _I, _I, _P],
     "qi_shard_destroy": [_P],
@@ -222,6 +226,14 @@ def w4a4_widen_codes_ex(codes, out_bytes, rows: int, k: int, stream=None) -> int
 def w4a4_quantize_activations_wide_ex(x, x_dtype: int, codes, scales, out_bytes, m: int, k: int, stream=None) -> int:
     return lib().qi_w4a4_quantize_activations_wide_ex(_p(x), x_dtype, _p(codes), _p(scales), _p(out_bytes), m, k,
                                                       _p(stream))
+
+
+def w4a4_swiglu_quantize_ex(gate, up, codes, scales, out_bytes, m: int, k: int, stream=None) -> int:
+    return lib().qi_w4a4_swiglu_quantize_ex(_p(gate), _p(up), _p(codes), _p(scales), _p(out_bytes), m, k, _p(stream))
+
+
+def w4a4_gelu_quantize_ex(x, codes, scales, out_bytes, m: int, k: int, stream=None) -> int:
+    return lib().qi_w4a4_gelu_quantize_ex(_p(x), _p(codes), _p(scales), _p(out_bytes), m, k, _p(stream))
 
 
 def w4a4_gemm_wide_ex(a_bytes, a_scales, w_bytes, w_scales, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,
@@ -413,6 +425,15 @@ def shard_plan(n: int, ranks: int, rank: int):
     return first.value, count.value
 
 
+def shard_plan_inputs(k: int, scheme: int, ranks: int, rank: int):
+    """(first_input, input_count) of the input columns `rank` owns in a row-parallel (K-sharded) linear."""
+    first, count = ctypes.c_int(0), ctypes.c_int(0)
+    status = lib().qi_shard_plan_inputs(k, scheme, ranks, rank, ctypes.byref(first), ctypes.byref(count))
+    if status != 0:
+        raise ValueError(f"k={k} cannot be split over {ranks} ranks in whole blocks of scheme {scheme} (status {status})")
+    return first.value, count.value
+
+
 def shard_unique_id() -> bytes:
     buffer = ctypes.create_string_buffer(SHARD_ID_BYTES)
     status = lib().qi_shard_unique_id(buffer)
@@ -448,6 +469,12 @@ class ShardContext:
         return lib().qi_shard_linear(self.handle, ctypes.byref(model.record), ctypes.byref(work.work), _p(input),
                                      input_dtype, _p(y_local), _p(y_slabs), output_dtype, rows, int(reuse_input),
                                      _p(stream))
+
+    def linear_inputs(self, model: PackedLinear, work: LinearWork, input_local, y, rows: int, reuse_input: bool = False, *,
+                      input_dtype: int = DTYPE_F32, stream=None) -> int:
+        """Row-parallel linear: partial product over this rank's inputs, summed over the ranks into float32 y [rows, n]."""
+        return lib().qi_shard_linear_inputs(self.handle, ctypes.byref(model.record), ctypes.byref(work.work), _p(input_local),
+                                            input_dtype, _p(y), rows, int(reuse_input), _p(stream))
 
     def destroy(self) -> int:
         if self.handle:

@@ -376,6 +376,26 @@ int qi_w4a4_quantize_activations_wide_ex(const void *x, int x_dtype, void *codes
                                                         static_cast<cudaStream_t>(stream)));
 }
 
+static int fused_quantize(int producer, const float *first, const float *second, void *codes, void *scales, void *bytes,
+                          int m, int k, void *stream) {
+    if (m < 0 || k <= 0 || k % 256 != 0) return INVALID;
+    if (m == 0) return 0;
+    if (!first || (producer == 1 && !second) || !scales || (!codes && !bytes)) return INVALID;
+    if (!aligned16(first) || (second && !aligned16(second)) || (bytes && !aligned16(bytes)) ||
+        (reinterpret_cast<uintptr_t>(codes) & 7) || (reinterpret_cast<uintptr_t>(scales) & 1))
+        return INVALID;
+    return static_cast<int>(launch_fused_quantize(producer, first, second, codes, scales, bytes, m, k, static_cast<cudaStream_t>(stream)));
+}
+
+int qi_w4a4_swiglu_quantize_ex(const float *gate, const float *up, void *codes, void *scales, void *bytes, int m, int k,
+                               void *stream) {
+    return fused_quantize(1, gate, up, codes, scales, bytes, m, k, stream);
+}
+
+int qi_w4a4_gelu_quantize_ex(const float *x, void *codes, void *scales, void *bytes, int m, int k, void *stream) {
+    return fused_quantize(2, x, nullptr, codes, scales, bytes, m, k, stream);
+}
+
 int qi_w4a4_widen_codes_ex(const void *codes, void *bytes, long long rows, int k, void *stream) {
     if (rows < 0 || k <= 0 || k % 32 != 0) return INVALID;
     if (rows == 0) return 0;

@@ -83,11 +83,40 @@ __device__ __forceinline__ void two_passes(float (&v)[16]) {
     for (int o = 0; o < 4; ++o) butterfly(v[o], v[o + 4], v[o + 8], v[o + 12]);
 }
 
+// What the quantiser reads. Plain: the activations themselves. The other two compute the activation on the
+// fly from what its producer would have read, with the producer's own expression, so that the [m, k] float32
+// matrix between the two kernels of the reference is never written or read:
+//   SwiGLU (qwen_image_cuda/cuda/ops.cu:133-138):    g / (1 + expf(-g)) * up
+//   GELU-tanh (qwen_image_cuda/cuda/ops.cu:155-160): 0.5 v (1 + tanhf(0.7978845608028654 (v + 0.044715 v v v)))
+template <typename T>
+struct PlainSource {
+    const T *x;
+    __device__ __forceinline__ void load(long long offset, float (&v)[16]) const { load16(x + offset, v); }
+};
+struct SwigluSource {
+    const float *gate, *up;
+    __device__ __forceinline__ void load(long long offset, float (&v)[16]) const {
+        float u[16];
+        load16(gate + offset, v);
+        load16(up + offset, u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+    }
+};
+struct GeluSource {
+    const float *x;
+    __device__ __forceinline__ void load(long long offset, float (&v)[16]) const {
+        load16(x + offset, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.5f * v[i] * (1.0f + tanhf(0.7978845608028654f * (v[i] + 0.044715f * v[i] * v[i] * v[i])));
+    }
+};
+
 // WIDE: also (or only, when codes is null) write every code as one FP8 E4M3 byte, [m, k], the
 // operand layout of w4a4_wide_gemm.cuh.
-template <typename T, bool WIDE>
+template <typename Source, bool WIDE>
 __global__ void __launch_bounds__(QUANT_THREADS)
-quantize_activations_kernel(const T *__restrict__ x, uint8_t *__restrict__ codes, __half *__restrict__ scales,
+quantize_activations_kernel(const Source source, uint8_t *__restrict__ codes, __half *__restrict__ scales,
                             uint8_t *__restrict__ bytes, long long chunks) {
     __shared__ __align__(16) float transpose[(QUANT_THREADS / 32) * 2 * REGION];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -98,7 +127,7 @@ quantize_activations_kernel(const T *__restrict__ x, uint8_t *__restrict__ codes
 
     float v[16];
     if (active) {
-        load16(x + chunk * 256 + l * 16, v);
+        source.load(chunk * 256 + l * 16, v);
     } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = 0.0f;
@@ -443,16 +472,37 @@ inline cudaError_t launch_quantize_activations(const void *x, int x_is_half, voi
         }
         return cudaGetLastError();
     }
+    const PlainSource<__half> from_half = {static_cast<const __half *>(x)};
+    const PlainSource<float> from_float = {static_cast<const float *>(x)};
     if (bytes != nullptr) {
-        if (x_is_half)
-            quantize_activations_kernel<__half, true><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __half *>(x), c, s, b, chunks);
-        else
-            quantize_activations_kernel<float, true><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float *>(x), c, s, b, chunks);
+        if (x_is_half) quantize_activations_kernel<PlainSource<__half>, true><<<grid, QUANT_THREADS, 0, stream>>>(from_half, c, s, b, chunks);
+        else quantize_activations_kernel<PlainSource<float>, true><<<grid, QUANT_THREADS, 0, stream>>>(from_float, c, s, b, chunks);
     } else {
-        if (x_is_half)
-            quantize_activations_kernel<__half, false><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const __half *>(x), c, s, b, chunks);
-        else
-            quantize_activations_kernel<float, false><<<grid, QUANT_THREADS, 0, stream>>>(static_cast<const float *>(x), c, s, b, chunks);
+        if (x_is_half) quantize_activations_kernel<PlainSource<__half>, false><<<grid, QUANT_THREADS, 0, stream>>>(from_half, c, s, b, chunks);
+        else quantize_activations_kernel<PlainSource<float>, false><<<grid, QUANT_THREADS, 0, stream>>>(from_float, c, s, b, chunks);
+    }
+    return cudaGetLastError();
+}
+
+// producer: 1 = SwiGLU of (first, second), 2 = GELU-tanh of first
+inline cudaError_t launch_fused_quantize(int producer, const float *first, const float *second, void *codes, void *scales,
+                                         void *bytes, int m, int k, cudaStream_t stream) {
+    const long long chunks = static_cast<long long>(m) * (k / 256);
+    if (chunks == 0) return cudaSuccess;
+    const int chunks_per_block = QUANT_THREADS / 16;
+    const long long blocks = (chunks + chunks_per_block - 1) / chunks_per_block;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const unsigned grid = static_cast<unsigned>(blocks);
+    uint8_t *c = static_cast<uint8_t *>(codes), *b = static_cast<uint8_t *>(bytes);
+    __half *s = static_cast<__half *>(scales);
+    const SwigluSource swiglu = {first, second};
+    const GeluSource gelu = {first};
+    if (producer == 1) {
+        if (bytes != nullptr) quantize_activations_kernel<SwigluSource, true><<<grid, QUANT_THREADS, 0, stream>>>(swiglu, c, s, b, chunks);
+        else quantize_activations_kernel<SwigluSource, false><<<grid, QUANT_THREADS, 0, stream>>>(swiglu, c, s, b, chunks);
+    } else {
+        if (bytes != nullptr) quantize_activations_kernel<GeluSource, true><<<grid, QUANT_THREADS, 0, stream>>>(gelu, c, s, b, chunks);
+        else quantize_activations_kernel<GeluSource, false><<<grid, QUANT_THREADS, 0, stream>>>(gelu, c, s, b, chunks);
     }
     return cudaGetLastError();
 }

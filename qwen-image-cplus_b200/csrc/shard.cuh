@@ -16,6 +16,8 @@
 #pragma once
 #include <dlfcn.h>
 
+#include <mutex>
+
 #include "../../include/qipack_b200.h"
 
 namespace qi {
@@ -42,7 +44,8 @@ struct Nccl {
 
 inline Nccl &nccl() {
     static Nccl api;
-    if (api.handle == nullptr) {
+    static std::once_flag once;
+    std::call_once(once, [] {
         const char *override_path = getenv("QI_NCCL_LIBRARY");
         const char *candidates[] = {override_path, "libnccl.so.2", "libnccl.so"};
         for (const char *name : candidates) {
@@ -58,7 +61,7 @@ inline Nccl &nccl() {
             api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
             api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
         }
-    }
+    });
     return api;
 }
 
@@ -68,24 +71,49 @@ struct Context {
     uint32_t magic;
     int rank, ranks, device;
     void *comm;
-    float *token;  // four bytes for the barrier's all-reduce; allocated by the first barrier
+    float *token;  // four bytes for the barrier's all-reduce
     // qi_shard_put_slice spreads its copies over these streams, so that several copy engines work at once
-    bool lanes_ready;
+    int lanes_made, joins_made;
+    bool fork_made;
     cudaStream_t lanes[PUT_LANES];
     cudaEvent_t fork, joins[PUT_LANES];
 };
+
+// Everything a context owns besides the communicator is made when it is created (nothing is allocated by the
+// calls that run on a stream) and taken down here, whatever part of it exists.
+inline void release(Context *c) {
+    if (c->token != nullptr) cudaFree(c->token);
+    for (int i = 0; i < c->lanes_made; ++i) cudaStreamDestroy(c->lanes[i]);
+    for (int i = 0; i < c->joins_made; ++i) cudaEventDestroy(c->joins[i]);
+    if (c->fork_made) cudaEventDestroy(c->fork);
+    c->token = nullptr, c->lanes_made = c->joins_made = 0, c->fork_made = false;
+}
+
+inline cudaError_t equip(Context *c) {
+    cudaError_t error = cudaMalloc(&c->token, sizeof(float));
+    if (error == cudaSuccess) error = cudaMemset(c->token, 0, sizeof(float));
+    for (int i = 0; i < PUT_LANES && error == cudaSuccess; ++i) {
+        error = cudaStreamCreateWithFlags(&c->lanes[i], cudaStreamNonBlocking);
+        if (error == cudaSuccess) c->lanes_made = i + 1, error = cudaEventCreateWithFlags(&c->joins[i], cudaEventDisableTiming);
+        if (error == cudaSuccess) c->joins_made = i + 1;
+    }
+    if (error == cudaSuccess) error = cudaEventCreateWithFlags(&c->fork, cudaEventDisableTiming);
+    if (error == cudaSuccess) c->fork_made = true;
+    return error;
+}
 
 typedef CUresult (*AddressRange)(CUdeviceptr *, size_t *, CUdeviceptr);
 
 inline AddressRange address_range() {
     static AddressRange function = nullptr;
-    if (function == nullptr) {
+    static std::once_flag once;
+    std::call_once(once, [] {
         void *entry = nullptr;
         cudaDriverEntryPointQueryResult result;
         if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &entry, cudaEnableDefault, &result) == cudaSuccess &&
             result == cudaDriverEntryPointSuccess)
             function = reinterpret_cast<AddressRange>(entry);
-    }
+    });
     return function;
 }
 static_assert(sizeof(cudaIpcMemHandle_t) == QI_SHARD_PEER_HANDLE_BYTES, "size of an exported handle");
@@ -103,6 +131,18 @@ inline int plan(int n, int ranks, int rank, int *first_row, int *row_count) {
     if (n % ranks != 0 || (n / ranks) % 128 != 0) return static_cast<int>(cudaErrorInvalidValue);
     if (first_row) *first_row = rank * (n / ranks);
     if (row_count) *row_count = n / ranks;
+    return 0;
+}
+
+// Input columns of an [n, k] weight that rank `rank` of `ranks` owns when the linear is split along K (row-parallel).
+// A slice must hold whole quantisation groups, and for scheme 6 whole 256-input Hadamard blocks, so that rotating
+// and quantising a slice of the activations gives the same codes as slicing the unsharded ones.
+inline int plan_inputs(int k, int scheme, int ranks, int rank, int *first_input, int *input_count) {
+    if (k <= 0 || ranks <= 0 || rank < 0 || rank >= ranks) return static_cast<int>(cudaErrorInvalidValue);
+    const int unit = scheme == QI_SCHEME_W4A4_H256 ? 256 : (scheme == QI_SCHEME_W4A16 ? 64 : 0);
+    if (unit == 0 || k % ranks != 0 || (k / ranks) % unit != 0) return static_cast<int>(cudaErrorInvalidValue);
+    if (first_input) *first_input = rank * (k / ranks);
+    if (input_count) *input_count = k / ranks;
     return 0;
 }
 
@@ -143,6 +183,16 @@ int qi_shard_create(void **context, int rank, int ranks, const void *id) {
         delete c;
         return NCCL_ERROR_BASE + result;
     }
+    if (ranks > 1) {
+        error = equip(c);
+        if (error != cudaSuccess) {
+            release(c);
+            if (api.CommAbort != nullptr) api.CommAbort(c->comm);
+            else api.CommDestroy(c->comm);
+            delete c;
+            return static_cast<int>(error);
+        }
+    }
     *context = c;
     return 0;
 }
@@ -152,14 +202,7 @@ int qi_shard_destroy(void *context) {
     Context *c = checked(context);
     if (c == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     const int result = c->comm ? nccl().CommDestroy(c->comm) : 0;
-    if (c->token != nullptr) cudaFree(c->token);
-    if (c->lanes_ready) {
-        for (int i = 0; i < PUT_LANES; ++i) {
-            cudaStreamDestroy(c->lanes[i]);
-            cudaEventDestroy(c->joins[i]);
-        }
-        cudaEventDestroy(c->fork);
-    }
+    release(c);
     c->magic = 0;
     delete c;
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
@@ -193,11 +236,7 @@ int qi_shard_barrier(void *context, void *stream) {
     if (c == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     if (c->ranks == 1) return 0;
     if (nccl().AllReduce == nullptr) return NCCL_MISSING;
-    if (c->token == nullptr) {
-        cudaError_t error = cudaMalloc(&c->token, sizeof(float));
-        if (error == cudaSuccess) error = cudaMemset(c->token, 0, sizeof(float));
-        if (error != cudaSuccess) return static_cast<int>(error);
-    }
+    if (c->token == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     const int result = nccl().AllReduce(c->token, c->token, 1, NCCL_FLOAT32, 0 /* ncclSum */, c->comm,
                                         static_cast<cudaStream_t>(stream));
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
@@ -214,23 +253,19 @@ int qi_shard_put_slice(void *context, void *const *y_copies, int copies, int out
     for (int i = 0; i < copies; ++i)
         if (y_copies[i] == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     if (copies == 1) return 0;
+    if (c->lanes_made != PUT_LANES || !c->fork_made) return static_cast<int>(cudaErrorInvalidValue);
     cudaError_t error = cudaSuccess;
-    if (!c->lanes_ready) {
-        for (int i = 0; i < PUT_LANES && error == cudaSuccess; ++i) {
-            error = cudaStreamCreateWithFlags(&c->lanes[i], cudaStreamNonBlocking);
-            if (error == cudaSuccess) error = cudaEventCreateWithFlags(&c->joins[i], cudaEventDisableTiming);
-        }
-        if (error == cudaSuccess) error = cudaEventCreateWithFlags(&c->fork, cudaEventDisableTiming);
-        if (error != cudaSuccess) return static_cast<int>(error);
-        c->lanes_ready = true;
-    }
     cudaStream_t caller = static_cast<cudaStream_t>(stream);
     const size_t element = output_dtype == QI_DTYPE_F16 ? 2 : 4;
     const size_t pitch = static_cast<size_t>(ldy) * element, first_byte = static_cast<size_t>(column) * element;
     const char *source = static_cast<const char *>(y_copies[c->rank]) + first_byte;
     const int lanes = copies - 1 < PUT_LANES ? copies - 1 : PUT_LANES;
     error = cudaEventRecord(c->fork, caller);
-    for (int i = 0; i < lanes && error == cudaSuccess; ++i) error = cudaStreamWaitEvent(c->lanes[i], c->fork, 0);
+    int forked = 0;  // lanes that wait for the caller's stream: they are joined back below whatever happens in between
+    for (int i = 0; i < lanes && error == cudaSuccess; ++i) {
+        error = cudaStreamWaitEvent(c->lanes[i], c->fork, 0);
+        if (error == cudaSuccess) forked = i + 1;
+    }
     for (int step = 1; step < copies && error == cudaSuccess; ++step) {
         const int peer = (c->rank + step) % copies;  // every rank starts with another GPU
         char *target = static_cast<char *>(y_copies[peer]) + first_byte;
@@ -241,9 +276,10 @@ int qi_shard_put_slice(void *context, void *const *y_copies, int copies, int out
             error = cudaMemcpy2DAsync(target, pitch, source, pitch, width, rows, cudaMemcpyDefault,
                                       c->lanes[(step - 1) % lanes]);
     }
-    for (int i = 0; i < lanes && error == cudaSuccess; ++i) {
-        error = cudaEventRecord(c->joins[i], c->lanes[i]);
-        if (error == cudaSuccess) error = cudaStreamWaitEvent(caller, c->joins[i], 0);
+    for (int i = 0; i < forked; ++i) {  // also after an error: copies already queued stay ordered before the caller's later work
+        cudaError_t joined = cudaEventRecord(c->joins[i], c->lanes[i]);
+        if (joined == cudaSuccess) joined = cudaStreamWaitEvent(caller, c->joins[i], 0);
+        if (error == cudaSuccess) error = joined;
     }
     return static_cast<int>(error);
 }
@@ -280,6 +316,28 @@ int qi_shard_peer_open(const void *handle, size_t offset, void **pointer) {
 int qi_shard_peer_close(void *pointer, size_t offset) {
     if (pointer == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     return static_cast<int>(cudaIpcCloseMemHandle(static_cast<char *>(pointer) - offset));
+}
+
+int qi_shard_plan_inputs(int k, int scheme, int ranks, int rank, int *first_input, int *input_count) {
+    return qi::shard::plan_inputs(k, scheme, ranks, rank, first_input, input_count);
+}
+
+int qi_shard_linear_inputs(void *context, const qi_packed_linear *local_record, const qi_linear_work *work,
+                           const void *input_local, int input_dtype, float *y, int rows, int reuse_input, void *stream) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr || local_record == nullptr || y == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    const int unit = local_record->scheme == QI_SCHEME_W4A4_H256 ? 256 : 64;
+    if (local_record->k % unit != 0) return static_cast<int>(cudaErrorInvalidValue);
+    if (c->ranks > 1 && local_record->bias != nullptr && c->rank != 0)
+        return static_cast<int>(cudaErrorInvalidValue);  // the bias is added once: give it to rank 0 only
+    const int status = qi_linear(local_record, work, input_local, input_dtype, y, QI_DTYPE_F32, local_record->n, rows,
+                                 reuse_input, stream);
+    if (status != 0 || c->ranks == 1) return status;
+    if (nccl().AllReduce == nullptr) return NCCL_MISSING;
+    const int result = nccl().AllReduce(y, y, static_cast<size_t>(rows) * local_record->n, NCCL_FLOAT32, 0 /* ncclSum */,
+                                        c->comm, static_cast<cudaStream_t>(stream));
+    return result == 0 ? 0 : NCCL_ERROR_BASE + result;
 }
 
 int qi_shard_linear(void *context, const qi_packed_linear *local_record, const qi_linear_work *work, const void *input,

@@ -122,6 +122,26 @@ def _worker(rank, ranks, port, result_path):
     expected5 = qo.w4a16_gemm(qo.f32_to_f16(x32).view(np.float16), codes5, scales5, minimums5)
     rebuilt5 = y_slabs.cpu().numpy().transpose(1, 0, 2).reshape(m, n).astype(np.float32)
     ok = ok and qt.max_relative_error(rebuilt5, expected5) <= 1e-3
+    # row-parallel (K-sharded) forms: this rank's input columns of every weight row and of the activations, partial
+    # products summed over the ranks (all-reduce, float32); whole Hadamard blocks / groups per slice
+    for scheme in (qi.SCHEME_W4A4_H256, qi.SCHEME_W4A16):
+        first_k, count_k = qi.shard_plan_inputs(k, scheme, ranks, rank)
+        x_slice = np.ascontiguousarray(x32[:, first_k:first_k + count_k])
+        if scheme == qi.SCHEME_W4A4_H256:
+            record_k = qi.PackedLinear(scheme, n, count_k, up(codes[:, first_k // 2:(first_k + count_k) // 2]),
+                                       up(scales[:, first_k // 64:(first_k + count_k) // 64]))
+            whole = expected
+        else:
+            record_k = qi.PackedLinear(scheme, n, count_k, up(codes5[:, first_k // 2:(first_k + count_k) // 2]),
+                                       up(scales5[:, first_k // 64:(first_k + count_k) // 64]),
+                                       up(minimums5[:, first_k // 64:(first_k + count_k) // 64]))
+            whole = expected5
+        y_sum = torch.full((m, n), float("nan"), dtype=torch.float32, device=device)
+        assert context.linear_inputs(record_k, work, up(x_slice), y_sum, m) == 0
+        torch.cuda.synchronize()
+        assert qi.kernel_status() == 0
+        bound = 1e-5 if scheme == qi.SCHEME_W4A4_H256 else 1e-3
+        ok = ok and qt.max_relative_error(y_sum.cpu().numpy(), whole) <= bound
     assert context.destroy() == 0
     dist.barrier()
     if rank == 0:

@@ -44,6 +44,23 @@ def test_shard_plan_rejects_illegal_splits(qi):
         qi.shard_plan(0, 1, 0)
 
 
+def test_input_plan_keeps_whole_hadamard_blocks_and_groups(qi):
+    # row-parallel split: scheme 6 slices are whole 256-input blocks, scheme 5 slices whole 64-groups
+    for k, scheme, ranks in ((12288, qi.SCHEME_W4A4_H256, 8), (3072, qi.SCHEME_W4A4_H256, 4), (3072, qi.SCHEME_W4A16, 8)):
+        covered = []
+        for rank in range(ranks):
+            first, count = qi.shard_plan_inputs(k, scheme, ranks, rank)
+            assert count % (256 if scheme == qi.SCHEME_W4A4_H256 else 64) == 0 and first == rank * count
+            covered.extend(range(first, first + count))
+        assert covered == list(range(k))
+    with pytest.raises(ValueError):
+        qi.shard_plan_inputs(3072, qi.SCHEME_W4A4_H256, 8, 0)   # 384 inputs per rank cut a Hadamard block in two
+    with pytest.raises(ValueError):
+        qi.shard_plan_inputs(3072, 3, 2, 0)                      # not a packed scheme
+    with pytest.raises(ValueError):
+        qi.shard_plan_inputs(3072, qi.SCHEME_W4A16, 2, 2)
+
+
 def test_placing_entry_points_reject_illegal_arguments_before_any_cuda_call(qi):
     """The argument checks of the entry points that place slices on other GPUs run on the host: they answer
     cudaErrorInvalidValue (1) without a device."""
@@ -64,6 +81,10 @@ def test_placing_entry_points_reject_illegal_arguments_before_any_cuda_call(qi):
     # a copy that is not aligned for whole 32-byte sectors
     odd = (ctypes.c_void_p * 2)(0x1000, 0x2010)
     assert scatter(fake, fake, fake, fake, None, odd, 2, 0, qi.DTYPE_F16, 512, 0, 128, 256, 256, None) == invalid
+    # scale arrays that the CTA-pair kernel cannot stage eight bytes at a time (it is the only kernel of this entry point)
+    scales_off = ctypes.c_void_p(0x1004)
+    assert scatter(fake, scales_off, fake, fake, None, copies, 2, 0, qi.DTYPE_F16, 512, 0, 128, 256, 256, None) == invalid
+    assert scatter(fake, fake, fake, scales_off, None, copies, 2, 0, qi.DTYPE_F16, 512, 0, 128, 256, 256, None) == invalid
     # not a context
     assert lib.qi_shard_put_slice(None, copies, 2, qi.DTYPE_F16, 512, 0, 128, 256, None) == invalid
     assert lib.qi_shard_barrier(None, None) == invalid
@@ -110,6 +131,18 @@ def _worker(rank, ranks, port, result_path):
     outputs["w4a16"] = (slabs_to_row_major(torch.stack(gathered5).numpy()),
                         qo.w4a16_gemm(x16, codes5, scales5, minimums5))
     ok = all(np.array_equal(a, b) for a, b in outputs.values())
+    # row-parallel: a slice of whole Hadamard blocks is quantised like the unsharded row, the partial products over
+    # the ranks' input slices add up to the unsharded result (float32 rounding of the partial sums apart)
+    first_k, count_k = qi.shard_plan_inputs(k, qi.SCHEME_W4A4_H256, ranks, rank)
+    slice_codes, slice_scales = qo.quantize_activations(x16[:, first_k:first_k + count_k])
+    ok = ok and np.array_equal(slice_codes, a_codes[:, first_k // 2:(first_k + count_k) // 2])
+    ok = ok and np.array_equal(slice_scales, a_scales[:, first_k // 64:(first_k + count_k) // 64])
+    partial = qo.w4a4_gemm(slice_codes, slice_scales, np.ascontiguousarray(codes[:, first_k // 2:(first_k + count_k) // 2]),
+                           np.ascontiguousarray(scales[:, first_k // 64:(first_k + count_k) // 64]))
+    total = torch.from_numpy(partial.copy())
+    dist.all_reduce(total)
+    whole = qo.w4a4_gemm(a_codes, a_scales, codes, scales)
+    ok = ok and float(np.max(np.abs(total.numpy() - whole))) <= 1e-5 * float(np.max(np.abs(whole)))
     dist.barrier()
     if rank == 0:
         with open(result_path, "w") as handle:
