@@ -19,8 +19,9 @@
 //     some 440 cycles, however deep the pipeline, but not those of other threads. So each team has
 //     two issuing threads (in different warps) that take turns group by group.
 //   * A fold warp copies its 32 x 32 dots of a group with one tcgen05.ld.32x32b.x32 (about 360
-//     B/clk/SM with eight warps; the 16x256b fragment shape reaches 230), hands the buffer back
-//     at once and then does the arithmetic from registers.
+//     B/clk/SM with eight warps; the 16x256b fragment shape reaches 230), computes half of the
+//     group's scale products while the copy is in flight, hands the buffer back and then does
+//     the rest of the arithmetic from registers.
 //   * A wait on a barrier whose phase is complete must cost one try_wait (25 cycles). A polling
 //     loop with a lane-0 / shuffle wrapper around it cost 230, several times per group.
 //   * Integer division costs a warp over a hundred cycles: the per-stage roles walk the
@@ -44,6 +45,61 @@
 
 namespace qi {
 namespace w4a4_pair {
+
+// Shared-window (32-bit) forms of the barrier and load helpers for the fold warps: their loop is short on
+// registers, and a generic 64-bit pointer costs two of them and an address conversion per use (measured on the
+// block workload: 660 -> 731 TOP/s from this change alone).
+__device__ __forceinline__ bool try_wait_u32(uint32_t barrier, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred P;\n\tmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\tselp.u32 %0, 1, 0, P;\n\t}\n"
+                 : "=r"(done) : "r"(barrier), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __noinline__ bool wait_slow_u32(uint32_t barrier, uint32_t parity, uint32_t code, uint32_t backoff_ns) {
+    for (uint32_t spin = 0; spin < WAIT_FAST_SPINS; ++spin) {
+        if (try_wait_u32(barrier, parity)) return true;
+        if (backoff_ns != 0) __nanosleep(backoff_ns);
+    }
+    const uint64_t start = global_timer_ns();
+    while (true) {
+        if (try_wait_u32(barrier, parity)) return true;
+        __nanosleep(128);
+        if (*reinterpret_cast<volatile uint32_t *>(&g_status) != 0) return false;
+        if (global_timer_ns() - start > WAIT_LIMIT_NS) break;
+    }
+    atomicCAS(&g_status, 0u, code);
+    return false;
+}
+__device__ __forceinline__ bool wait_warp_u32(uint32_t barrier, uint32_t parity, uint32_t code, int lane, uint32_t backoff_ns) {
+    if (__all_sync(0xffffffffu, try_wait_u32(barrier, parity))) return true;
+    uint32_t ok = 1;
+    if (lane == 0) ok = wait_slow_u32(barrier, parity, code, backoff_ns) ? 1u : 0u;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ ulonglong2 lds_pairs(uint32_t address) {
+    ulonglong2 value;
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(value.x), "=l"(value.y) : "r"(address));
+    return value;
+}
+__device__ __forceinline__ float lds_f32(uint32_t address) {
+    float value;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(value) : "r"(address));
+    return value;
+}
+__device__ __forceinline__ void arrive_u32(uint32_t barrier) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(barrier) : "memory");
+}
+// The wait for a 32-register copy out of TMEM, with the registers tied to it: nothing that uses them can be
+// scheduled before it, while work that does not need them may sit between the copy and the wait.
+__device__ __forceinline__ void tmem_load_wait_32(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
+          "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+          "+r"(r[30]), "+r"(r[31])
+        :: "memory");
+}
 
 constexpr int TEAMS = 2;       // independent fold pipelines, each with its own half of the columns
 constexpr int THREADS = 768;
@@ -77,6 +133,9 @@ constexpr uint32_t AHEAD_BACKOFF_NS = 256;
 // warps that are behind included (measured: 588 -> 660 TOP/s on the block when the waiting is done by one
 // lane per warp with a pause between polls; a try_wait with a suspend-time hint instead was slower, 572).
 constexpr uint32_t FOLD_BACKOFF_NS = 200, MMA_BACKOFF_NS = 64;
+// Columns whose scale products sa * sw a fold thread computes while its copy of the dots out of TMEM is still in
+// flight (measured on 4096 x 9216 x 3072: 0 -> 295 us, 16 -> 293 .. 288, more than 16 no better: registers).
+constexpr int HOIST = 16;
 constexpr int SCALE_AHEAD = 3, SCALE_RING = 4;  // stages of scales in flight; ring slots
 
 constexpr int A_HALF_BYTES = BM * 128, B_HALF_BYTES = (BN / 2) * 128;  // one 128-byte-wide slab of a stage
@@ -249,9 +308,10 @@ __device__ __forceinline__ void mma_role(const View &v, uint32_t mine) {
 
 // Warps 8-23: a warp folds 32 rows x 32 columns of this CTA's half of the tile; a thread owns one
 // row (its TMEM lane) and 32 accumulators.
-// Per group a warp waits for the dots, copies its 32 x 32 of them into registers with one
-// tcgen05.ld.32x32b.x32 (the shape with the highest TMEM read rate), hands the buffer back and
-// then does the arithmetic; the other three warps of its scheduler fill the waits.
+// Per group a warp waits for the dots, starts the copy of its 32 x 32 of them into registers (one
+// tcgen05.ld.32x32b.x32, the shape with the highest TMEM read rate), computes the scale products
+// of its first HOIST columns meanwhile, hands the buffer back once the copy has landed and then
+// does the arithmetic; the other three warps of its scheduler fill the waits.
 // All lanes need the same weight scales: one 16-byte broadcast load per four columns.
 // The arithmetic is the packed fp32 pair form of  acc = fma(dot, sa * sw, acc): each half is
 // IEEE-rounded exactly like the scalar instruction, so the result has the reference's bits.
@@ -262,37 +322,46 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
     static_assert(COLUMNS == 32, "one tcgen05.ld.32x32b.x32 per warp and group");
     // The hardware ties a warp to the TMEM lanes 32 * (warp % 4); four consecutive warps make one column slice.
     const int quadrant = warp & 3, slice = (warp - FOLD_WARP0) >> 2, team = slice / (TEAM_COLUMNS / COLUMNS);
-    const uint64_t *dot_full = v.dot_full + team * BUFFERS;
+    const uint32_t dot_full = smem_u32(v.dot_full + team * BUFFERS);
     const uint32_t leader_dot_empty = map_to_cta(smem_u32(v.dot_empty + team * BUFFERS), 0);
     const uint32_t tmem_lane = v.tmem_base + team * BUFFERS * TEAM_COLUMNS + (slice % (TEAM_COLUMNS / COLUMNS)) * COLUMNS +
                                (static_cast<uint32_t>(quadrant * 32) << 16);
+    const uint32_t sw_base = smem_u32(v.sw_tile) + slice * COLUMNS * 4;
+    const uint32_t sa_base = smem_u32(v.sa_tile) + (quadrant * 32 + lane) * 16;
+    const uint32_t scale_ready = smem_u32(v.scale_ready), empty = smem_u32(v.empty);
     uint32_t dots[COLUMNS];  // dots[j] = dot of this thread's row and column j of the warp's 32
-    // A wait starts with one try_wait by every lane (all the warp pays when the phase is complete); only when that
-    // fails does lane 0 poll, with pauses. A wait that ran out of time sets `failed`; the warp looks at it once per stage.
     bool alive = true, failed = false;
-    uint32_t iteration = 0, group_count = 0;
+    uint32_t s = 0, phase = 0, group_count = 0;
     for (int tile = v.pair; tile < v.tiles && alive; tile += v.pairs) {
         const int row = (tile % v.tiles_m) * 2 * BM + static_cast<int>(v.cta) * BM + quadrant * 32 + lane;
         const int n0 = (tile / v.tiles_m) * BN + slice * COLUMNS;
         uint64_t acc[COLUMNS / 2];  // acc[j] = columns 2 j, 2 j + 1
 #pragma unroll
         for (int j = 0; j < COLUMNS / 2; ++j) acc[j] = 0;
-        for (int ks = 0; ks < v.k_stages && alive; ++ks, ++iteration) {
-            const int s = iteration % STAGES;
-            const uint32_t phase = (iteration / STAGES) & 1;
+        for (int ks = 0; ks < v.k_stages && alive; ++ks) {
             if (__any_sync(0xffffffffu, failed)) { alive = false; break; }
-            failed = !mbarrier_wait_warp(&v.scale_ready[s], phase, &g_status, STATUS_WAIT_READY | 0x5000 | s, lane, FOLD_BACKOFF_NS);
-            const float *sw_stage = v.sw_tile + s * STAGE_GROUPS * BN + slice * COLUMNS;
-            const float4 sa_quad = v.sa_tile[s * BM + quadrant * 32 + lane];
+            failed = !wait_warp_u32(scale_ready + s * 8, phase, STATUS_WAIT_READY | 0x5000 | s, lane, FOLD_BACKOFF_NS);
+            const uint32_t sw_stage = sw_base + s * SW_BYTES;
 #pragma unroll
             for (int gl = 0; gl < STAGE_GROUPS; ++gl, ++group_count) {
                 const uint32_t buffer = group_count % BUFFERS;
-                failed |= !mbarrier_wait_warp(const_cast<uint64_t *>(&dot_full[buffer]), (group_count / BUFFERS) & 1, &g_status,
-                                              STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane, FOLD_BACKOFF_NS);
+                failed |= !wait_warp_u32(dot_full + buffer * 8, (group_count / BUFFERS) & 1,
+                                         STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane, FOLD_BACKOFF_NS);
                 tcgen05_fence_after();
                 tmem_load_32x32(tmem_lane + buffer * TEAM_COLUMNS, dots);
-                tmem_load_wait();
-                // this warp's share of the buffer is in registers: hand it back to the leader's MMA threads
+                // while the copy is in flight: the scale products of the first HOIST columns
+                const float scale = lds_f32(sa_base + s * SA_BYTES + gl * 4);
+                const uint64_t sa2 = pack_f32x2(scale, scale);
+                const uint32_t sw_group = sw_stage + gl * BN * 4;
+                uint64_t p[HOIST / 2];
+#pragma unroll
+                ulonglong2 sw4;
+                for (int q = 0; q < HOIST / 4; ++q) {
+                    sw4 = lds_pairs(sw_group + 16 * q);
+                    p[2 * q] = mul_f32x2(sa2, sw4.x);
+                    p[2 * q + 1] = mul_f32x2(sa2, sw4.y);
+                }
+                tmem_load_wait_32(dots);
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbarrier_arrive_cluster(leader_dot_empty + buffer * 8);
@@ -303,20 +372,21 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
                             dots_out[(static_cast<size_t>(row) * shape.n + n0 + j) * v.groups + ks * STAGE_GROUPS + gl] =
                                 static_cast<int32_t>(__uint_as_float(dots[j]));
                 }
-                const float scale = gl == 0 ? sa_quad.x : gl == 1 ? sa_quad.y : gl == 2 ? sa_quad.z : sa_quad.w;
-                const uint64_t sa2 = pack_f32x2(scale, scale);
-                const float *sw_group = sw_stage + gl * BN;
 #pragma unroll
-                for (int q = 0; q < COLUMNS / 4; ++q) {
-                    const ulonglong2 sw4 = *reinterpret_cast<const ulonglong2 *>(sw_group + 4 * q);  // four columns, as two pairs
+                for (int q = 0; q < HOIST / 4; ++q) {
+                    acc[2 * q] = fma_f32x2(pack_u32x2(dots[4 * q], dots[4 * q + 1]), p[2 * q], acc[2 * q]);
+                    acc[2 * q + 1] = fma_f32x2(pack_u32x2(dots[4 * q + 2], dots[4 * q + 3]), p[2 * q + 1], acc[2 * q + 1]);
+                }
+#pragma unroll
+                for (int q = HOIST / 4; q < COLUMNS / 4; ++q) {
+                    sw4 = lds_pairs(sw_group + 16 * q);  // four columns, as two pairs
                     acc[2 * q] = fma_f32x2(pack_u32x2(dots[4 * q], dots[4 * q + 1]), mul_f32x2(sa2, sw4.x), acc[2 * q]);
                     acc[2 * q + 1] = fma_f32x2(pack_u32x2(dots[4 * q + 2], dots[4 * q + 3]), mul_f32x2(sa2, sw4.y), acc[2 * q + 1]);
                 }
-            }
-            if (alive) {
-                __syncwarp();
-                if (lane == 0) mbarrier_arrive(&v.empty[s]);  // done with this stage's scales; its codes were consumed before the dots arrived
-            }
+                        }
+            __syncwarp();
+            if (lane == 0) arrive_u32(empty + s * 8);  // done with this stage's scales; its codes were consumed before the dots arrived
+            if (++s == STAGES) s = 0, phase ^= 1;
         }
         if (!alive) break;
         if (row >= shape.m) continue;
