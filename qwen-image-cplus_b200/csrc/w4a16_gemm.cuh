@@ -58,20 +58,42 @@ struct Tile {
 };
 
 // 32 packed nibbles (16 bytes) -> 32 fp16 values in input order.
+// Byte b of a word holds codes 2b (low nibble) and 2b + 1. The fast path puts each code into mantissa bits 4..7 of
+// an fp16 with a zero exponent field, i.e. the subnormal code * 2^-20, and lets ONE fused multiply-add per pair do
+// the rest: fma(code * 2^-20, scale * 2^20, minimum) = fp16(code * scale + minimum), the product exact and the
+// sum rounded once like the reference's (gemm.cu:223-230). It needs scale * 2^20 to be an fp16 number: |scale| < 1/16.
+// Any other scale (a NaN included) takes the path that first makes each code an fp16 integer.
 __device__ __forceinline__ void unpack32(const uint4 packed, const __half2 scale2, const __half2 minimum2,
                                          uint4 (&out)[4]) {
     const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
-    const __half2 offsets = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x5400));  // (1024, 64)
     uint32_t values[16];
+    const __half sixteenth = __ushort_as_half(0x2C00), two_to_10 = __ushort_as_half(0x6400);
+    if (__hlt(__habs(__low2half(scale2)), sixteenth)) {
+        const __half2 up = __half2half2(two_to_10);
+        const __half2 scale_up = __hmul2(__hmul2(scale2, up), up);
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t low_nibbles_up = words[w] << 4;
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const uint32_t spread = __byte_perm(words[w], 0u, 0x4040u + 0x0101u * b);  // [byte b, 0, byte b, 0]
-            uint32_t magic = (spread & 0x00F0000Fu) | 0x54006400u;
-            const __half2 code = __hsub2(*reinterpret_cast<__half2 *>(&magic), offsets);
-            const __half2 weight = __hfma2(code, scale2, minimum2);
-            values[4 * w + b] = *reinterpret_cast<const uint32_t *>(&weight);
+            for (int b = 0; b < 4; ++b) {
+                // [byte b of the shifted word, -, byte b of the word, -], then the two nibbles in bits 4..7 and 20..23
+                uint32_t pair = __byte_perm(low_nibbles_up, words[w], 0x4400u + 0x1111u * b) & 0x00F000F0u;
+                const __half2 weight = __hfma2(*reinterpret_cast<__half2 *>(&pair), scale_up, minimum2);
+                values[4 * w + b] = *reinterpret_cast<const uint32_t *>(&weight);
+            }
+        }
+    } else {
+        const __half2 offsets = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x5400));  // (1024, 64)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t spread = __byte_perm(words[w], 0u, 0x4040u + 0x0101u * b);  // [byte b, 0, byte b, 0]
+                uint32_t magic = (spread & 0x00F0000Fu) | 0x54006400u;
+                const __half2 code = __hsub2(*reinterpret_cast<__half2 *>(&magic), offsets);
+                const __half2 weight = __hfma2(code, scale2, minimum2);
+                values[4 * w + b] = *reinterpret_cast<const uint32_t *>(&weight);
+            }
         }
     }
 #pragma unroll
