@@ -709,6 +709,242 @@ def run_block(args):
     return result
 
 
+# ---- the W4A4 block with paired splits (N > 1, --parallel pairs) ------------------------------------------
+
+def run_block_pairs(args):
+    """The block with the splits paired the way the block's data flow allows, so that no wide tensor is gathered:
+    qkv and fc1 are split by output columns and their slices stay on their GPU (attention works on whole heads, the
+    activation function on elements); out and fc2 are split by INPUT columns - the slice a GPU computed in the linear
+    before is the slice it needs - and their float32 partial results are summed over the GPUs (all-reduce) and stored
+    as fp16. Where an input split would cut a 256-input Hadamard block (out at 8 GPUs: 384 inputs per GPU) the
+    linear falls back to output columns with an all-gather. The sums run on a second stream under the next kernels."""
+    job = Job(args)
+    torch, qi, device, world, rank = job.torch, job.qi, job.device, job.world, job.rank
+    context, stream, handle = job.context, job.stream, job.handle
+    assert context is not None, "--parallel pairs is a multi-GPU mode"
+    m = args.m
+    generator = torch.Generator(device=device)
+    generator.manual_seed(1234)
+    layers, full = [], []
+    for name, n, k, kind in LINEARS:
+        w_codes, w_scales = make_packed_w4a4(torch, generator, n, k, device)
+        x = make_activations(torch, generator, m, k, kind, device)
+        split = "columns" if name in ("qkv", "fc1") else "inputs"
+        if split == "inputs":
+            try:
+                k_lo, k_local = qi.shard_plan_inputs(k, qi.SCHEME_W4A4_H256, world, rank)
+            except ValueError:
+                split = "columns+gather"
+        if split == "inputs":
+            n_local, lo = n, 0
+            w_local = w_codes[:, k_lo // 2:(k_lo + k_local) // 2].contiguous()
+            scales_local = w_scales[:, k_lo // 64:(k_lo + k_local) // 64].contiguous()
+            x_local = x[:, k_lo:k_lo + k_local].contiguous()
+        else:
+            k_lo, k_local = 0, k
+            lo, n_local = qi.shard_plan(n, world, rank)
+            w_local = w_codes[lo:lo + n_local].contiguous()
+            scales_local = w_scales[lo:lo + n_local].contiguous()
+            x_local = x
+        w_wide = torch.empty(n_local, k_local, dtype=torch.uint8, device=device)
+        assert qi.w4a4_widen_codes_ex(w_local, w_wide, n_local, k_local) == 0
+        layers.append({
+            "name": name, "n": n, "k": k, "split": split, "n_local": n_local, "lo": lo, "k_lo": k_lo, "k_local": k_local,
+            "x": x_local, "w_wide": w_wide, "w_scales": scales_local,
+            "a_wide": torch.empty(m, k_local, dtype=torch.uint8, device=device),
+            "a_scales": torch.empty(m, k_local // 64, dtype=torch.float16, device=device),
+            "y_local": torch.empty(m, n_local, dtype=torch.float16, device=device) if split != "inputs" else None,
+            "y_sum": torch.empty(m, n, dtype=torch.float32, device=device) if split == "inputs" else None,
+            "y_half": torch.empty(m, n, dtype=torch.float16, device=device) if split == "inputs" else None,
+            "y_all": torch.empty(world, m, n_local, dtype=torch.float16, device=device) if split == "columns+gather" else None,
+        })
+        full.append((w_codes, w_scales, x))
+    torch.cuda.synchronize()
+    launches = {"count": 0}
+    side = torch.cuda.Stream(device=device)
+
+    def step(index, events=None, slot=None):
+        for layer in layers:
+            k_local, n_local = layer["k_local"], layer["n_local"]
+            x_in = layer["x"] if slot is None else layer["x_slots"][slot]
+            assert qi.w4a4_quantize_activations_wide_ex(x_in, qi.DTYPE_F16, None, layer["a_scales"], layer["a_wide"], m, k_local, handle) == 0
+            if layer.get("summed") is not None:
+                stream.wait_event(layer["summed"])  # the previous sum or gather has read this linear's output buffer
+            if events is not None:
+                start = torch.cuda.Event(enable_timing=True)
+                start.record(stream)
+            if layer["split"] == "inputs":
+                status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"], None,
+                                              layer["y_sum"], qi.DTYPE_F32, n_local, m, n_local, k_local, handle)
+            else:
+                y_out = layer["y_local"] if slot is None else layer["y_slots"][slot]
+                status = qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"], None,
+                                              y_out, qi.DTYPE_F16, n_local, m, n_local, k_local, handle)
+            assert status == 0, f"gemm {layer['name']}: cuda status {status}"
+            if events is not None:
+                stop = torch.cuda.Event(enable_timing=True)
+                stop.record(stream)
+                events.append((start, stop, layer))
+            launches["count"] += 2
+            if layer["split"] == "columns":
+                continue
+            computed = torch.cuda.Event()
+            computed.record(stream)
+            side.wait_event(computed)
+            if layer["split"] == "inputs":
+                status = context.all_reduce(layer["y_sum"], m * layer["n"], side.cuda_stream)
+                y_half = layer["y_half"] if slot is None else layer["y_slots"][slot]
+                status = status or qi.f32_to_f16_ex(layer["y_sum"], y_half, m * layer["n"], side.cuda_stream)
+                launches["count"] += 1
+            else:
+                status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, side.cuda_stream)
+            assert status == 0, f"sum or gather {layer['name']}: status {status}"
+            layer["summed"] = torch.cuda.Event()
+            layer["summed"].record(side)
+        stream.wait_stream(side)  # a step ends when its last sum has arrived everywhere
+
+    for index in range(args.warmup):
+        step(index)
+    job.barrier()
+    assert qi.kernel_status() == 0, "a kernel gave up on a wait during warm-up"
+
+    # What each rank holds equals the unsharded kernels on its own GPU: column slices bit for bit, the summed linears
+    # to the rounding of `world` float32 partial sums and one fp16 store.
+    worst = 0.0
+    for layer, (w_codes, w_scales, x) in zip(layers, full):
+        n, k = layer["n"], layer["k"]
+        scales = torch.empty(m, k // 64, dtype=torch.float16, device=device)
+        expected = torch.empty(m, n, dtype=torch.float16, device=device)
+        a_wide = torch.empty(m, k, dtype=torch.uint8, device=device)
+        w_wide = torch.empty(n, k, dtype=torch.uint8, device=device)
+        assert qi.w4a4_quantize_activations_wide_ex(x, qi.DTYPE_F16, None, scales, a_wide, m, k, handle) == 0
+        assert qi.w4a4_widen_codes_ex(w_codes, w_wide, n, k, handle) == 0
+        assert qi.w4a4_gemm_wide_ex(a_wide, scales, w_wide, w_scales, None, expected, qi.DTYPE_F16, n, m, n, k, handle) == 0
+        stream.synchronize()
+        if layer["split"] == "inputs":
+            got, want = layer["y_half"].float(), expected.float()
+            error = float(((got - want).abs() / (want.abs() + 1e-3 * want.abs().max())).max())
+            worst = max(worst, error)
+            assert error <= 2e-3, f"{layer['name']}: the summed output is {error:.2e} away from the unsharded one on rank {rank}"
+        elif layer["split"] == "columns":
+            assert torch.equal(layer["y_local"], expected[:, layer["lo"]:layer["lo"] + layer["n_local"]]), \
+                f"{layer['name']}: the column slice differs from the unsharded output on rank {rank}"
+        else:
+            assert torch.equal(layer["y_all"].permute(1, 0, 2).reshape(m, n), expected), \
+                f"{layer['name']}: the gathered output differs from the unsharded one on rank {rank}"
+        del expected, scales, a_wide, w_wide
+    full.clear()
+    torch.cuda.empty_cache()
+    job.barrier()
+    verified = (f"on every one of {world} ranks: column slices bit-equal to the unsharded kernels, summed linears within "
+                f"{worst:.1e} relative of them (float32 partial sums in NCCL's order, one fp16 store)")
+
+    launches["count"] = 0
+    gemm_events = []
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(job.local_rank) as sampler:
+        job.barrier()
+        begin.record(stream)
+        for index in range(args.steps):
+            step(args.warmup + index, gemm_events)
+        end.record(stream)
+        job.barrier()
+        elapsed_ms = begin.elapsed_time(end)
+        timed_launches = launches["count"]
+        assert qi.kernel_status() == 0, "a kernel gave up on a wait during the timed region"
+        gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events)
+        gemm_ops = sum(2.0 * m * layer["n_local"] * layer["k_local"] for _, _, layer in gemm_events)
+
+        # end to end: every rank brings in the inputs it needs (its input slice for the summed linears) and takes out
+        # what it produced (its column slice, or its share of the rows of a summed output), every step
+        host_x = [layer["x"].cpu().pin_memory() for layer in layers]
+        rows = m // world
+        host_y = [torch.empty((rows, layer["n"]) if layer["split"] == "inputs" else (m, layer["n_local"]), dtype=torch.float16).pin_memory()
+                  for layer in layers]
+        h2d = sum(t.numel() * t.element_size() for t in host_x)
+        d2h = sum(t.numel() * t.element_size() for t in host_y)
+        for layer in layers:
+            layer["x_slots"] = [torch.empty_like(layer["x"]) for _ in range(2)]
+            layer["y_slots"] = [torch.empty_like(layer["y_half"] if layer["split"] == "inputs" else layer["y_local"]) for _ in range(2)]
+        in_stream, out_stream = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+        computed, copied_out = [None, None], [None, None]
+
+        def e2e_step(index):
+            slot = index % 2
+            if computed[slot] is not None:
+                in_stream.wait_event(computed[slot])
+            with torch.cuda.stream(in_stream):
+                for layer, hx in zip(layers, host_x):
+                    layer["x_slots"][slot].copy_(hx, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(in_stream)
+            stream.wait_event(arrived)
+            if copied_out[slot] is not None:
+                stream.wait_event(copied_out[slot])
+            step(index, slot=slot)
+            computed[slot] = torch.cuda.Event()
+            computed[slot].record(stream)
+            out_stream.wait_event(computed[slot])
+            with torch.cuda.stream(out_stream):
+                for layer, hy in zip(layers, host_y):
+                    source = layer["y_slots"][slot]
+                    hy.copy_(source[rank * rows:(rank + 1) * rows] if layer["split"] == "inputs" else source, non_blocking=True)
+            copied_out[slot] = torch.cuda.Event()
+            copied_out[slot].record(out_stream)
+
+        e2e_steps = max(4, min(args.steps, 20))
+        for index in range(4):
+            e2e_step(index)
+        job.barrier()
+        e2e_begin, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_begin.record(in_stream)
+        for index in range(e2e_steps):
+            e2e_step(index)
+        out_stream.wait_stream(stream)
+        out_stream.wait_stream(in_stream)
+        e2e_end.record(out_stream)
+        job.barrier()
+        e2e_ms = e2e_begin.elapsed_time(e2e_end)
+
+    elapsed_ms, e2e_ms, gemm_ms = job.max_over_ranks([elapsed_ms, e2e_ms, gemm_ms])
+    result = None
+    if rank == 0:
+        peaks = measured_peaks()
+        tensor_peaks = tensor_peaks_now(qi)
+        ops_per_step = block_ops(m)
+        achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12
+        splits = ", ".join(f"{layer['name']}: {layer['split']}" for layer in layers)
+        result = {
+            "metric": METRIC, "value": ops_per_step * args.steps / (elapsed_ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "int4 codes (one E4M3 byte each), exact fp32 tensor-core group dots, fp32 fold",
+            "data": "synthetic: W ~ N(0,0.02) rotated (H256) and quantised to int4 g64 on the device, "
+                    "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
+            "config": {"workload": workload_text(m), "name": args.workload, "m": m, "ops_per_step": ops_per_step,
+                       "w4a4_path": "wide", "outputs": "fp16",
+                       "parallelism": f"paired splits x{world} ({splits}); float32 partial results summed by NCCL all-reduce on a "
+                                      "second stream, then stored as fp16; activation quantiser on each rank's own inputs",
+                       "l2": "per-step working set exceeds the 126 MB L2"},
+            "gpu_launches": timed_launches,
+            "e2e": {"value": ops_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "roofline": {"kernel": "w4a4_pair::gemm_kernel", "bound": "tensor", "achieved": achieved, "peak": tensor_peaks["e4m3"],
+                         "unit": "TOP/s", "frac": achieved / tensor_peaks["e4m3"],
+                         "frac_of_2x_bf16_burst": achieved / (2.0 * peaks["bf16_burst"]),
+                         "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_sustained"]),
+                         "traffic": NCU_TRAFFIC_BYTES_QKV_M4096 * (m / 4096.0) / world,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the qkv launch at "
+                                           "M=4096 (its 2MNK is the average of the four launches), scaled by rows and ranks",
+                         "peak_source": tensor_peaks["how"] + f"; bf16 figures of MEASURED_PEAKS.json ({peaks['source']})",
+                         "tensor_peaks_measured_now": {key: tensor_peaks[key] for key in ("f16", "e4m3", "s8")},
+                         "launches_timed": len(gemm_events), "avg_launch_ms": gemm_ms / max(1, len(gemm_events))},
+            "clocks": sampler.summary(), "verified": verified,
+        }
+    job.close()
+    return result
+
+
 # ---- the 60-block stacks (workloads c3 and c5) ------------------------------------------------------
 
 def run_stack(args):
@@ -934,6 +1170,10 @@ def main():
                         help="N > 1: how the column slices reach every GPU. nccl (auto): an all-gather after each GEMM; fused: the "
                              "GEMM's epilogue stores its slice into every GPU's output over NVLink, a barrier follows; copy: the copy "
                              "engines carry the slice to every GPU, a barrier follows; slabs: the same with outputs [ranks][rows][N/ranks]")
+    parser.add_argument("--parallel", default="columns", choices=["columns", "pairs"],
+                        help="N > 1, block workloads: columns: every linear split by output columns and its slices gathered (the "
+                             "default); pairs: qkv and fc1 by output columns without a gather, out and fc2 by input columns with an "
+                             "all-reduce of the float32 partial results")
     parser.add_argument("--shard-quantiser", action="store_true",
                         help="N > 1: every rank quantises its share of the rows and the codes and scales are all-gathered, "
                              "instead of every rank quantising all rows (measured slower on 2 GPUs: two more NCCL launches "
@@ -951,7 +1191,8 @@ def main():
         if result is not None:
             print(json.dumps(result), flush=True)
         return
-    result = run_stack(args) if stack else run_block(args)
+    pairs = args.parallel == "pairs" and not stack and int(os.environ.get("WORLD_SIZE", "1")) > 1
+    result = run_stack(args) if stack else run_block_pairs(args) if pairs else run_block(args)
     if result is None:
         return
     if not args.no_cpu_baseline and result["n_gpus"] == 1:

@@ -80,6 +80,9 @@ int qi_w4a4_quantize_activations_ex(const void *x, int x_dtype, void *codes, voi
 int qi_w4a4_gemm_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
                     const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
 
+/* qi_f32_to_f16 on a stream. */
+int qi_f32_to_f16_ex(const float *source, void *out, unsigned long long count, void *stream);
+
 /* Any m >= 1: rows beyond the last multiple of 128 are handled in the kernel; m <= 8 takes
  * the GEMV path below. */
 int qi_w4a16_gemm_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
@@ -300,6 +303,10 @@ int qi_shard_linear(void *context, const qi_packed_linear *local_record, const q
  * sum over ranks is a float32 sum in NCCL's order: the result agrees with the unsharded operator to float32
  * rounding of R partial sums, not bit for bit. A bias may be given on rank 0 only. */
 int qi_shard_plan_inputs(int k, int scheme, int ranks, int rank, int *first_input, int *input_count);
+/* The sum over ranks by itself, in place, on `stream`: y [count] float32 <- sum of every rank's y. For callers that
+ * run the partial product themselves (qi_w4a4_gemm_wide_ex and the like on an input slice, float32 output) and want
+ * the sum on another stream, under the next linear's kernels. No counterpart in the reference (single GPU). */
+int qi_shard_all_reduce_f32(void *context, float *y, unsigned long long count, void *stream);
 int qi_shard_linear_inputs(void *context, const struct qi_packed_linear *local_record, const struct qi_linear_work *work,
                            const void *input_local, int input_dtype, float *y, int rows, int reuse_input, void *stream);
 

@@ -88,6 +88,7 @@ SIGNATURES = {
     "qi_w4a4_gemm": [_P, _P, _P, _P, _P, _I, _I, _I],
     "qi_w4a16_gemm": [_P, _P, _P, _P, _P, _I, _I, _I],
     "qi_f32_to_f16": [_P, _P, _ULL],
+    "qi_f32_to_f16_ex": [_P, _P, _ULL, _P],
     "qi_w4a4_quantize_activations_ex": [_P, _I, _P, _P, _I, _I, _P],
     "qi_w4a4_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
     "qi_w4a16_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
@@ -109,6 +110,7 @@ SIGNATURES = {
     "qi_shard_destroy": [_P],
     "qi_shard_rank": [_P, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
     "qi_shard_all_gather": [_P, _P, _P, _I, _I, _I, _P],
+    "qi_shard_all_reduce_f32": [_P, _P, ctypes.c_ulonglong, _P],
     "qi_shard_barrier": [_P, _P],
     "qi_shard_put_slice": [_P, ctypes.POINTER(ctypes.c_void_p), _I, _I, _LL, _I, _I, _I, _P],
     "qi_shard_peer_export": [_P, _P, ctypes.POINTER(ctypes.c_size_t)],
@@ -184,6 +186,10 @@ def w4a16_gemm(x_half, codes, scales, minimums, y, m: int, n: int, k: int) -> in
 
 def f32_to_f16(source, out, count: int) -> int:
     return lib().qi_f32_to_f16(_p(source), _p(out), count)
+
+
+def f32_to_f16_ex(source, out, count: int, stream=None) -> int:
+    return lib().qi_f32_to_f16_ex(_p(source), _p(out), count, _p(stream))
 
 
 # ---- extended forms ------------------------------------------------------------------------------
@@ -455,6 +461,10 @@ class ShardContext:
 
     def all_gather(self, y_local, y_slabs, output_dtype: int, rows: int, n_local: int, stream=None) -> int:
         return lib().qi_shard_all_gather(self.handle, _p(y_local), _p(y_slabs), output_dtype, rows, n_local, _p(stream))
+
+    def all_reduce(self, y, count: int, stream=None) -> int:
+        """y [count] float32 <- the sum over the ranks, in place."""
+        return lib().qi_shard_all_reduce_f32(self.handle, _p(y), count, _p(stream))
 
     def put_slice(self, copies, output_dtype: int, ldy: int, column: int, rows: int, n_local: int, stream=None) -> int:
         return lib().qi_shard_put_slice(self.handle, copies, len(copies), output_dtype, ldy, column, rows, n_local,

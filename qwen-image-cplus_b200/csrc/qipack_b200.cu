@@ -513,6 +513,12 @@ int qi_f32_to_f16(const float *source, void *out, unsigned long long count) {
     return static_cast<int>(launch_f32_to_f16(source, out, count, nullptr));
 }
 
+int qi_f32_to_f16_ex(const float *source, void *out, unsigned long long count, void *stream) {
+    if (count == 0) return 0;
+    if (!source || !out) return INVALID;
+    return static_cast<int>(launch_f32_to_f16(source, out, count, static_cast<cudaStream_t>(stream)));
+}
+
 int qi_w4a16_dequantize_ex(const void *codes, const void *scales, const void *minimums, void *w_half, int n, int k,
                            void *stream) {
     if (n <= 0 || k <= 0 || k % 64 != 0) return INVALID;

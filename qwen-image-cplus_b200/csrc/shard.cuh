@@ -230,6 +230,17 @@ int qi_shard_all_gather(void *context, const void *y_local, void *y_slabs, int o
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
 }
 
+int qi_shard_all_reduce_f32(void *context, float *y, unsigned long long count, void *stream) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr || y == nullptr || count == 0) return static_cast<int>(cudaErrorInvalidValue);
+    if (c->ranks == 1) return 0;
+    if (nccl().AllReduce == nullptr) return NCCL_MISSING;
+    const int result = nccl().AllReduce(y, y, static_cast<size_t>(count), NCCL_FLOAT32, 0 /* ncclSum */, c->comm,
+                                        static_cast<cudaStream_t>(stream));
+    return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
 int qi_shard_barrier(void *context, void *stream) {
     using namespace qi::shard;
     Context *c = checked(context);

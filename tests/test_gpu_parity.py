@@ -128,6 +128,12 @@ def test_f32_to_f16_bit_exact(qi):
         assert qi.f32_to_f16(up(x), out, count) == 0
         torch.cuda.synchronize()
         assert np.array_equal(half_bits(out), qo.f32_to_f16(x))
+        on_stream = torch.zeros(count, dtype=torch.float16, device="cuda")
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        assert qi.f32_to_f16_ex(up(x), on_stream, count, stream.cuda_stream) == 0
+        stream.synchronize()
+        assert np.array_equal(half_bits(on_stream), qo.f32_to_f16(x))
 
 
 # ---- W4A16 ---------------------------------------------------------------------------------------

@@ -142,6 +142,11 @@ def _worker(rank, ranks, port, result_path):
         assert qi.kernel_status() == 0
         bound = 1e-5 if scheme == qi.SCHEME_W4A4_H256 else 1e-3
         ok = ok and qt.max_relative_error(y_sum.cpu().numpy(), whole) <= bound
+    # the sum over ranks by itself
+    part = torch.full((1000,), float(rank + 1), dtype=torch.float32, device=device)
+    assert context.all_reduce(part, part.numel()) == 0
+    torch.cuda.synchronize()
+    ok = ok and bool((part == float(sum(range(1, ranks + 1)))).all())
     assert context.destroy() == 0
     dist.barrier()
     if rank == 0:
