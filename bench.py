@@ -229,8 +229,10 @@ def other_kernels(qi, torch, device, stream, peaks, tensor_peaks, m):
                                   "frac_of_bf16_sustained": achieved / peaks["bf16_sustained"],
                                   "peak_source": tensor_peaks["how"]}
 
-    # the four symbols the reference binds run this kernel: nibble-packed codes, int8 tensor-core dots
-    packed, ops, seconds = [], 0.0, 0.0
+    # The entry points the reference binds, on its operand format (nibble-packed codes). By shape they widen both operands
+    # into scratch memory of the stream's pool and run the byte-operand kernel on CTA pairs; the int8 kernel that widens
+    # the nibbles in shared memory is timed beside it.
+    packed, ops, seconds, int8_seconds = [], 0.0, 0.0, 0.0
     for name, n, k, _ in LINEARS:
         def signed_codes(rows):  # two codes in -7..7 per byte (-8 is not a code of the format)
             values = torch.randint(-7, 8, (rows, k), dtype=torch.int16, device=device, generator=generator) & 0xF
@@ -241,12 +243,18 @@ def other_kernels(qi, torch, device, stream, peaks, tensor_peaks, m):
         a_scales = (torch.rand(m, k // 64, device=device, generator=generator) * 0.5 + 0.05).half()
         y = torch.empty(m, n, dtype=torch.float16, device=device)
         ms = graph_timed(torch, stream, lambda i: qi.w4a4_gemm_ex(a_codes, a_scales, w_codes, w_scales, None, y, qi.DTYPE_F16, n, m, n, k, handle), 10)
+        int8_ms = graph_timed(torch, stream, lambda i: qi.w4a4_gemm_path_ex(a_codes, a_scales, w_codes, w_scales, None, y, qi.DTYPE_F16, n, m, n, k,
+                                                                             qi.W4A4_PATH_INT8, handle), 10)
         ops += 2.0 * m * n * k
         seconds += ms * 1e-3
-        packed.append({"linear": name, "ms": ms, "tops": 2.0 * m * n * k / ms / 1e9})
+        int8_seconds += int8_ms * 1e-3
+        packed.append({"linear": name, "ms": ms, "tops": 2.0 * m * n * k / ms / 1e9, "int8_kernel_ms": int8_ms})
         del w_codes, a_codes, w_scales, a_scales, y
-    out["w4a4_packed"] = {"kernel": "w4a4::gemm_kernel (qi_w4a4_gemm, the drop-in ABI)", "linears": packed,
-                          "tops": ops / seconds / 1e12, "frac_of_int8_mma_loop": ops / seconds / 1e12 / tensor_peaks["s8"]}
+    out["w4a4_packed"] = {"kernel": "qi_w4a4_gemm_ex (the drop-in ABI, nibble-packed operands): two widening kernels into (m + n) k bytes of "
+                                    "pool scratch, then w4a4_pair::gemm_kernel; int8_kernel: w4a4::gemm_kernel on the nibbles",
+                          "linears": packed, "tops": ops / seconds / 1e12, "frac_of_e4m3_mma_loop": ops / seconds / 1e12 / tensor_peaks["e4m3"],
+                          "int8_kernel_tops": ops / int8_seconds / 1e12,
+                          "int8_kernel_frac_of_int8_mma_loop": ops / int8_seconds / 1e12 / tensor_peaks["s8"]}
 
     n, k = GEMV_N, GEMV_K
     copies = [make_packed_w4a16(torch, generator, n, k, device) for _ in range(8)]  # 8 x 31.9 MB: none is in L2 at its turn

@@ -91,6 +91,7 @@ SIGNATURES = {
     "qi_f32_to_f16_ex": [_P, _P, _ULL, _P],
     "qi_w4a4_quantize_activations_ex": [_P, _I, _P, _P, _I, _I, _P],
     "qi_w4a4_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
+    "qi_w4a4_gemm_path_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _P],
     "qi_w4a16_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
     "qi_w4a16_gemv_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
     "qi_w4a16_dequantize_ex": [_P, _P, _P, _P, _I, _I, _P],
@@ -202,6 +203,15 @@ def w4a4_gemm_ex(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype: int, ld
                  stream=None) -> int:
     return lib().qi_w4a4_gemm_ex(_p(a_codes), _p(a_scales), _p(w_codes), _p(w_scales), _p(bias), _p(y), y_dtype,
                                  ldy, m, n, k, _p(stream))
+
+
+W4A4_PATH_BY_SHAPE, W4A4_PATH_INT8, W4A4_PATH_WIDENED = 0, 1, 2
+
+
+def w4a4_gemm_path_ex(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,
+                      path: int, stream=None) -> int:
+    return lib().qi_w4a4_gemm_path_ex(_p(a_codes), _p(a_scales), _p(w_codes), _p(w_scales), _p(bias), _p(y), y_dtype,
+                                      ldy, m, n, k, path, _p(stream))
 
 
 def w4a16_gemm_ex(x_half, codes, scales, minimums, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,

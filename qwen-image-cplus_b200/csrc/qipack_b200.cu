@@ -313,19 +313,6 @@ int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const 
     }
 }
 
-int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales, const float *bias,
-              void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n, int k, cudaStream_t stream) {
-    if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 128 != 0) return INVALID;
-    if (!a_codes || !a_scales || !w_codes || !w_scales) return INVALID;
-    if (!aligned16(a_codes) || !aligned16(w_codes) || (reinterpret_cast<uintptr_t>(a_scales) & 3) ||
-        (reinterpret_cast<uintptr_t>(w_scales) & 3) || !output_ok(y, y_dtype, ldy, n))
-        return INVALID;
-    const int device = current_device();
-    if (device < 0) return INVALID;
-    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
-    return launch_w4a4<128, 4>(a_codes, a_scales, w_codes, w_scales, bias, y, dots, shape, stream, device);
-}
-
 // single_cta: always the one-CTA kernel (128 x 128 tiles); otherwise CTA pairs where the shape and pointers allow.
 int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_bytes, const void *w_scales,
                    const float *bias, void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n, int k,
@@ -344,6 +331,45 @@ int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_byte
     if (single_cta || k % w4a4_pair::STAGE_K != 0 || !scales_aligned8)
         return launch_w4a4_wide<6>(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
     return launch_w4a4_pair(a_bytes, a_scales, w_bytes, w_scales, bias, y, dots, shape, stream, device);
+}
+
+// The W4A4 GEMM on nibble-packed codes (the reference's operand format). `path`: 1 = the int8 kernel that widens the
+// nibbles in shared memory; 2 = both operands widened to one byte per code in scratch memory of the stream's pool
+// (two small kernels), then the byte-operand kernel on CTA pairs, which is the faster GEMM by more than the
+// widening costs once the matrices are large; 0 = 2 where the pair kernel takes the shape, else 1. Same bits on
+// every path. The scratch is (m + n) * k bytes from cudaMallocAsync and goes back with cudaFreeAsync, both in
+// stream order; if the pool refuses, path 0 falls back to 1.
+constexpr int W4A4_PATHS = 3;
+int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales, const float *bias,
+              void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n, int k, int path, cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 128 != 0 || path < 0 || path >= W4A4_PATHS) return INVALID;
+    if (!a_codes || !a_scales || !w_codes || !w_scales) return INVALID;
+    if (!aligned16(a_codes) || !aligned16(w_codes) || (reinterpret_cast<uintptr_t>(a_scales) & 3) ||
+        (reinterpret_cast<uintptr_t>(w_scales) & 3) || !output_ok(y, y_dtype, ldy, n))
+        return INVALID;
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
+    const bool scales_aligned8 = ((reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(w_scales)) & 7) == 0;
+    const bool pair_takes_it = dots == nullptr && k % w4a4_pair::STAGE_K == 0 && scales_aligned8;
+    if (path == 2 && !pair_takes_it) return INVALID;
+    if (path == 2 || (path == 0 && pair_takes_it && m >= 256 && n >= 256)) {
+        const size_t a_bytes = (static_cast<size_t>(m) * k + 255) & ~static_cast<size_t>(255);
+        const size_t w_bytes = static_cast<size_t>(n) * k;
+        uint8_t *scratch = nullptr;
+        const cudaError_t allocated = cudaMallocAsync(reinterpret_cast<void **>(&scratch), a_bytes + w_bytes, stream);
+        if (allocated == cudaSuccess) {
+            int status = qi_w4a4_widen_codes_ex(a_codes, scratch, m, k, stream);
+            if (status == 0) status = qi_w4a4_widen_codes_ex(w_codes, scratch + a_bytes, n, k, stream);
+            if (status == 0)
+                status = launch_w4a4_pair(scratch, a_scales, scratch + a_bytes, w_scales, bias, y, nullptr, shape, stream, device);
+            const cudaError_t freed = cudaFreeAsync(scratch, stream);
+            return status != 0 ? status : static_cast<int>(freed);
+        }
+        (void)cudaGetLastError();  // the refusal is not the caller's error
+        if (path == 2) return static_cast<int>(allocated);
+    }
+    return launch_w4a4<128, 4>(a_codes, a_scales, w_codes, w_scales, bias, y, dots, shape, stream, device);
 }
 
 }  // namespace
@@ -465,20 +491,26 @@ int qi_w4a4_quantize_activations(const float *x, void *codes, void *scales, int 
 
 int qi_w4a4_gemm_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
                     const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
-    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k,
+    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k, 0,
+                     static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a4_gemm_path_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
+                         const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, int path, void *stream) {
+    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k, path,
                      static_cast<cudaStream_t>(stream));
 }
 
 int qi_w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales, float *y,
                  int m, int n, int k) {
     if (m % 128 != 0 || n % 128 != 0 || k % 256 != 0) return INVALID;  // gemm.cu:185
-    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, nullptr, y, QI_DTYPE_F32, n, nullptr, m, n, k, nullptr);
+    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, nullptr, y, QI_DTYPE_F32, n, nullptr, m, n, k, 0, nullptr);
 }
 
 int qi_w4a4_group_dots_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
                           float *y, int32_t *dots, int m, int n, int k, void *stream) {
     if (dots == nullptr) return INVALID;
-    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, nullptr, y, QI_DTYPE_F32, n, dots, m, n, k,
+    return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, nullptr, y, QI_DTYPE_F32, n, dots, m, n, k, 1,
                      static_cast<cudaStream_t>(stream));
 }
 

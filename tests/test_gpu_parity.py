@@ -339,6 +339,33 @@ def test_w4a4_gemm_block_shape_sampled(qi):
     assert np.array_equal(got[rows], expected)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 384, 512), (512, 256, 3072), (200, 256, 768), (256, 256, 640)])
+def test_w4a4_gemm_paths_give_the_same_bits(qi, m, n, k):
+    """The packed-operand entry point on each of its kernels: the int8 kernel on nibbles, and both operands widened
+    into scratch memory for the byte-operand kernel on CTA pairs (twice in a row: the scratch is taken and returned
+    in stream order)."""
+    rng = np.random.default_rng(4500 + m + n + k)
+    if k % 256 == 0:
+        w_codes, w_scales = qt.pack_w4a4(qt.make_weights(rng, n, k))
+        a_codes, a_scales = qo.quantize_activations(qt.make_activations(rng, m, k))
+    else:  # not a length the H256 format has, but one the int8 kernel takes (two groups per stage)
+        w_codes, w_scales = qt.random_w4a4_pack(rng, n, k, 1e-3, 6e-3)
+        a_codes, a_scales = qt.random_w4a4_pack(rng, m, k, 0.05, 0.6)
+    bias = qt.make_bias(rng, n)
+    expected = qo.w4a4_gemm(a_codes, a_scales, w_codes, w_scales, bias=bias)
+    args = (up(a_codes), up(a_scales), up(w_codes), up(w_scales), up(bias))
+    paths = [qi.W4A4_PATH_INT8, qi.W4A4_PATH_BY_SHAPE] + ([qi.W4A4_PATH_WIDENED] * 2 if k % 256 == 0 else [])
+    for path in paths:
+        y = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        assert qi.w4a4_gemm_path_ex(*args, y, qi.DTYPE_F32, n, m, n, k, path) == 0
+        check_status(qi)
+        assert np.array_equal(y.cpu().numpy(), expected), path
+    y = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    assert qi.w4a4_gemm_path_ex(*args, y, qi.DTYPE_F32, n, m, n, k, 3) == qi.CUDA_ERROR_INVALID_VALUE
+    if k % 256 != 0:  # the pair kernel's stage is four groups
+        assert qi.w4a4_gemm_path_ex(*args, y, qi.DTYPE_F32, n, m, n, k, qi.W4A4_PATH_WIDENED) == qi.CUDA_ERROR_INVALID_VALUE
+
+
 def test_w4a4_gemm_rejects_what_the_reference_rejects(qi):  # gemm.cu:185
     t = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     assert qi.w4a4_gemm(t, t, t, t, t, 100, 128, 256) == qi.CUDA_ERROR_INVALID_VALUE
