@@ -80,6 +80,25 @@ int qi_w4a4_quantize_activations_ex(const void *x, int x_dtype, void *codes, voi
 int qi_w4a4_gemm_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
                     const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
 
+/* qi_w4a4_gemm_ex on its widened path (path 2 below) without taking memory from anywhere: the widened operands go
+ * into a fixed array of QI_NOALLOC_SCRATCH_BYTES that is part of the library's device code, one instance per device.
+ * For callers that may not allocate while they run: a process whose device memory is handed out completely at start
+ * (a serving engine's arena, a memory pool pinned to a budget), or code that runs where even a stream-ordered
+ * allocation is unwelcome because its timing must not depend on the state of a pool. It makes no cudaMalloc,
+ * cudaMallocAsync, cudaFree or library call that allocates.
+ *   - m, n, k as for path 2 (k % 256 == 0, n % 32 == 0, scale arrays 8-byte aligned), and
+ *     round_up(m * k, 256) + n * k <= QI_NOALLOC_SCRATCH_BYTES, else QI_NOALLOC_TOO_LARGE and nothing is launched
+ *     (64 MiB takes the block's qkv, out and fc1 linears at 4096 rows; fc2, 88 MB, is too large).
+ *   - The first call on a device looks up the address of that device's array (cudaGetSymbolAddress, with the device
+ *     current) and keeps it; make that call before any stream capture begins.
+ *   - One array per device: calls on the same device that overlap in time (different streams or host threads) race
+ *     on it. Calls on one stream follow each other and are safe. Nothing in the array has to be cleared.
+ * Same bits as qi_w4a4_gemm_ex. No counterpart in the reference (its kernel needs no scratch, gemm.cu:65-189). */
+#define QI_NOALLOC_SCRATCH_BYTES (64u << 20)
+#define QI_NOALLOC_TOO_LARGE 30001
+int qi_w4a4_gemm_noalloc_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
+                            const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
+
 /* As qi_w4a4_gemm_ex with the kernel chosen by the caller instead of by shape (for tests and tuning; every path gives
  * the same bits): 0 = by shape; 1 = the int8 kernel that widens the nibbles in shared memory (any k % 128 == 0);
  * 2 = both operands widened to one byte per code in scratch memory, then the byte-operand kernel on CTA pairs

@@ -501,6 +501,48 @@ int qi_w4a4_gemm_path_ex(const void *a_codes, const void *a_scales, const void *
                      static_cast<cudaStream_t>(stream));
 }
 
+}  // extern "C"
+
+// ---- the packed W4A4 GEMM for callers that must not allocate ------------------------------------------------------
+// The widened operands of qi_w4a4_gemm_noalloc_ex live in this array instead of pool memory. One array per device
+// (the runtime gives every device its own instance of a __device__ variable), shared by every call on that device:
+// calls that overlap in time - two streams, two host threads - write over each other's operands. Nothing in it has
+// to start at zero: a call writes every byte it later reads, so there is nothing to clear between calls.
+constexpr size_t NOALLOC_SCRATCH_BYTES = static_cast<size_t>(QI_NOALLOC_SCRATCH_BYTES);
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+extern "C" {
+
+int qi_w4a4_gemm_noalloc_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
+                            const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
+    if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % w4a4_pair::STAGE_K != 0) return INVALID;
+    if (!a_codes || !a_scales || !w_codes || !w_scales) return INVALID;
+    if (!aligned16(a_codes) || !aligned16(w_codes) || !output_ok(y, y_dtype, ldy, n)) return INVALID;
+    if (((reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(w_scales)) & 7) != 0) return INVALID;
+    const size_t a_bytes = (static_cast<size_t>(m) * k + 255) & ~static_cast<size_t>(255);
+    const size_t w_bytes = static_cast<size_t>(n) * k;
+    if (a_bytes + w_bytes > NOALLOC_SCRATCH_BYTES) return QI_NOALLOC_TOO_LARGE;
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    // Set-up, once per device, with that device current: where this device's instance of the array is. It happens in
+    // the first call on the device, which may also be what makes the runtime load this library's device code; make
+    // that call before any stream capture begins.
+    static std::atomic<uint8_t *> address[MAX_DEVICES];
+    uint8_t *scratch = address[device].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
+        const cudaError_t found = cudaGetSymbolAddress(reinterpret_cast<void **>(&scratch), g_noalloc_scratch);
+        if (found != cudaSuccess) return static_cast<int>(found);
+        if (scratch == nullptr) return INVALID;
+        address[device].store(scratch, std::memory_order_release);
+    }
+    const cudaStream_t on = static_cast<cudaStream_t>(stream);
+    int status = qi_w4a4_widen_codes_ex(a_codes, scratch, m, k, stream);
+    if (status == 0) status = qi_w4a4_widen_codes_ex(w_codes, scratch + a_bytes, n, k, stream);
+    if (status != 0) return status;
+    const GemmShape shape = {m, n, k, ldy, y_dtype == QI_DTYPE_F16};
+    return launch_w4a4_pair(scratch, a_scales, scratch + a_bytes, w_scales, bias, y, nullptr, shape, on, device);
+}
+
 int qi_w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales, float *y,
                  int m, int n, int k) {
     if (m % 128 != 0 || n % 128 != 0 || k % 256 != 0) return INVALID;  // gemm.cu:185
