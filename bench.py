@@ -975,27 +975,39 @@ def run_stack(args):
     k_max = max(k for _, _, k, _ in LINEARS)
     policy_counts = {"w4a4": 0, "w4a16": 0}
 
-    def make_record(n, k):
+    def make_record(n, k, keep_whole):
+        """This rank's shard of a fresh random record, and (keep_whole, N > 1) the whole record for the check below."""
         scheme6 = args.workload == "c5" and host_random.random() < 0.7
         lo, n_local = qi.shard_plan(n, world, rank)
+        whole = None
         if scheme6:
             policy_counts["w4a4"] += 1
-            codes, scales = make_packed_w4a4(torch, generator, n, k, device)
-            codes, scales = codes[lo:lo + n_local].contiguous(), scales[lo:lo + n_local].contiguous()
+            all_codes, all_scales = make_packed_w4a4(torch, generator, n, k, device)
+            codes, scales = all_codes[lo:lo + n_local].contiguous(), all_scales[lo:lo + n_local].contiguous()
             wide = torch.empty(n_local, k, dtype=torch.uint8, device=device)
             assert qi.w4a4_widen_codes_ex(codes, wide, n_local, k) == 0
-            return qi.PackedLinear(qi.SCHEME_W4A4_H256, n_local, k, codes, scales, weights_wide=wide)
+            if keep_whole:
+                all_wide = torch.empty(n, k, dtype=torch.uint8, device=device)
+                assert qi.w4a4_widen_codes_ex(all_codes, all_wide, n, k) == 0
+                whole = qi.PackedLinear(qi.SCHEME_W4A4_H256, n, k, all_codes, all_scales, weights_wide=all_wide)
+            return qi.PackedLinear(qi.SCHEME_W4A4_H256, n_local, k, codes, scales, weights_wide=wide), whole
         policy_counts["w4a16"] += 1
         codes, scales, minimums = make_packed_w4a16(torch, generator, n, k, device)
+        if keep_whole:
+            whole = qi.PackedLinear(qi.SCHEME_W4A16, n, k, codes, scales, minimums)
         return qi.PackedLinear(qi.SCHEME_W4A16, n_local, k, codes[lo:lo + n_local].contiguous(),
-                               scales[lo:lo + n_local].contiguous(), minimums[lo:lo + n_local].contiguous())
+                               scales[lo:lo + n_local].contiguous(), minimums[lo:lo + n_local].contiguous()), whole
 
     plan = []  # (record, stream index, linear index)
+    whole_records = []  # the last block's records unsharded, with their place: what the gathered outputs are checked against
     gemv_records = []
-    for _ in range(blocks):
+    for block in range(blocks):
         for stream_index in range(len(streams)):
             for linear_index, (_, n, k, _) in enumerate(LINEARS):
-                plan.append((make_record(n, k), stream_index, linear_index))
+                record, whole = make_record(n, k, world > 1 and block == blocks - 1)
+                plan.append((record, stream_index, linear_index))
+                if whole is not None:
+                    whole_records.append((whole, stream_index, linear_index))
         for _ in range(gemvs_per_block):
             gemv_records.append(make_packed_w4a16(torch, generator, GEMV_N, GEMV_K, device))
     inputs, outputs, works, slabs = [], [], [], []
@@ -1037,6 +1049,24 @@ def run_stack(args):
             step()
     job.barrier()
     assert qi.kernel_status() == 0, "a kernel gave up on a wait during warm-up"
+    verified = None
+    if context is not None:
+        # The slabs hold what the last block left: gathered, they equal the same dispatcher on the whole record on this
+        # rank's own GPU, bit for bit (the buffers are reused block after block, so the last block is what can be checked).
+        for whole, stream_index, linear_index in whole_records:
+            rows = streams[stream_index][1]
+            expected = torch.empty(rows, whole.n, dtype=torch.float16, device=device)
+            assert qi.linear(whole, works[stream_index], inputs[stream_index][linear_index], expected, rows,
+                             input_dtype=qi.DTYPE_F16, output_dtype=qi.DTYPE_F16, stream=handle) == 0
+            stream.synchronize()
+            got = slabs[stream_index][linear_index].permute(1, 0, 2).reshape(rows, whole.n)
+            assert torch.equal(got, expected), f"stream {stream_index} linear {linear_index}: the gathered output differs on rank {rank}"
+            del expected
+        whole_records.clear()
+        torch.cuda.empty_cache()
+        job.barrier()
+        verified = (f"gathered outputs of the last block's {len(streams) * len(LINEARS)} linears bit-equal to the unsharded "
+                    f"dispatcher on every one of {world} ranks")
     launches["count"] = 0
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(job.local_rank) as sampler:
@@ -1100,6 +1130,8 @@ def run_stack(args):
                          "tensor_peaks_measured_now": {key: tensor_peaks[key] for key in ("f16", "e4m3", "s8")}},
             "clocks": sampler.summary(),
         }
+        if verified is not None:
+            result["verified"] = verified
     job.close()
     return result
 
