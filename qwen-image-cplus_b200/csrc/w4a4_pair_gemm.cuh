@@ -13,8 +13,14 @@
 //   * Warps that wait on the same barrier run in lock step: all copy dots out of TMEM at the same
 //     time (queueing at the TMEM read port), then all multiply at the same time. So the tile's 128
 //     columns are split into two TEAMS of 64, each a pipeline of its own: own MMAs (N = 64), own
-//     four TMEM buffers, own barriers, own eight fold warps per CTA. The teams drift apart and one
+//     two TMEM buffers, own barriers, own eight fold warps per CTA. The teams drift apart and one
 //     fills the other's gaps.
+//   * The fold warps set the pace (a count of their waits: the dots are ready at the first look in
+//     every one of 768 groups, while the MMA threads wait for a free buffer 99 % of the time), so
+//     what a fold warp does per hand-off counts: a TMEM buffer holds the dots of TWO groups (one
+//     128-byte slab of K: four MMAs, one commit), which halves the looks at the barrier and the
+//     hand-backs (760 -> 807 TOP/s on the block), and a look is one try_wait by every lane
+//     without a vote around it (-> 823).
 //   * A tcgen05.commit holds up the later tcgen05 instructions of the THREAD that issued it for
 //     some 440 cycles, however deep the pipeline, but not those of other threads. So each team has
 //     two issuing threads (in different warps) that take turns group by group.
@@ -22,8 +28,8 @@
 //     B/clk/SM with eight warps; the 16x256b fragment shape reaches 230), computes half of the
 //     group's scale products while the copy is in flight, hands the buffer back and then does
 //     the rest of the arithmetic from registers.
-//   * A wait on a barrier whose phase is complete must cost one try_wait (25 cycles). A polling
-//     loop with a lane-0 / shuffle wrapper around it cost 230, several times per group.
+//   * A wait on a barrier whose phase is complete must cost one try_wait. A polling loop with a
+//     lane-0 / shuffle wrapper around it cost 230 cycles, a try_wait with a vote about 100.
 //   * Integer division costs a warp over a hundred cycles: the per-stage roles walk the
 //     (tile, stage) sequence incrementally. Scales reach the fold threads as fp32 in shared memory,
 //     staged by two warps with cp.async several stages ahead. The TMA has a thread of its own: when
@@ -36,7 +42,7 @@
 //   warp 0      one thread: TMA for own A rows and own B rows
 //   warps 1, 2  stage the scales (sw: the tile's 128 columns; sa: this CTA's 128 rows; four groups per stage)
 //   warps 4-7   leader only, one thread each: tcgen05.mma.cta_group::2 kind::f8f6f4 (two K = 32 steps
-//               per group) and the commit that arrives on both CTAs' barriers
+//               per group, two groups per buffer) and the commit that arrives on both CTAs' barriers
 //   warps 8-23  fold this CTA's 128 rows x 128 columns, 32 rows x 32 columns per warp
 //   (warp 3 only gives up its registers: setmaxnreg works on groups of four warps)
 #pragma once
@@ -108,7 +114,8 @@ constexpr int BN = 128;        // columns of the pair's tile; each CTA loads 64 
 constexpr int STAGE_K = 256;   // bytes (= codes) of K per pipeline stage: four groups, as two 128-byte swizzle rows
 constexpr int STAGE_GROUPS = STAGE_K / 64, K_HALVES = STAGE_K / 128;
 constexpr int TEAM_COLUMNS = BN / TEAMS;
-constexpr int BUFFERS = 4;     // TMEM buffers of TEAM_COLUMNS fp32 columns per team
+constexpr int BUFFERS = 2;     // TMEM buffers per team, each the dots of TWO groups (one 128-byte slab of K): 2 x TEAM_COLUMNS columns
+constexpr int BUFFER_COLUMNS = 2 * TEAM_COLUMNS;
 constexpr int STAGES = 4;
 constexpr int TURNS = 2;       // MMA-issuing threads per team, taking turns group by group
 constexpr int PRODUCER_WARP = 0, SW_WARP = 1, SA_WARP = 2, MMA_WARP0 = 4, MMA_WARPS = TURNS * TEAMS, FOLD_WARP0 = 8, FOLD_WARPS = 16;  // warp 3 idle
@@ -280,38 +287,41 @@ __device__ __forceinline__ void scale_role(const View &v, const __half *__restri
 }
 
 // Warps 4-7 of the leader, one thread each. Thread `mine` serves team (mine % TEAMS) and multiplies the
-// groups whose running number is (mine / TEAMS) modulo TURNS into that team's TMEM buffers: N = 64
-// columns per MMA. A group's number fixes everything else: its pipeline stage (four groups per stage, in two 128-byte slabs) and
-// its buffer.
+// slabs (128 bytes of K = two groups) whose running number is (mine / TEAMS) modulo TURNS into that team's TMEM
+// buffers: N = 64 columns per MMA, the slab's first group into the buffer's first 64 columns, the second into the
+// other 64. A slab's number fixes everything else: its pipeline stage (two slabs per stage) and its buffer.
 __device__ __forceinline__ void mma_role(const View &v, uint32_t mine) {
     constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * BM, TEAM_COLUMNS);
     const int my_tiles = v.pair < v.tiles ? (v.tiles - 1 - v.pair) / v.pairs + 1 : 0;
-    const uint32_t total_groups = static_cast<uint32_t>(my_tiles) * v.groups;
+    const uint32_t total_slabs = static_cast<uint32_t>(my_tiles) * v.groups / 2;  // a slab: 128 bytes of K = two groups
     const uint32_t team = mine % TEAMS, turn = mine / TEAMS;
     uint64_t *dot_full = v.dot_full + team * BUFFERS, *dot_empty = v.dot_empty + team * BUFFERS;
-    for (uint32_t group = turn; group < total_groups; group += TURNS) {
-        const uint32_t iteration = group / STAGE_GROUPS, half = (group % STAGE_GROUPS) >> 1, gl = group & 1;
+    for (uint32_t slab = turn; slab < total_slabs; slab += TURNS) {
+        const uint32_t iteration = slab / K_HALVES, half = slab % K_HALVES;
         const uint32_t s = iteration % STAGES, phase = (iteration / STAGES) & 1;
-        const uint32_t buffer = group % BUFFERS, buffer_phase = (group / BUFFERS) & 1;
+        const uint32_t buffer = slab % BUFFERS, buffer_phase = (slab / BUFFERS) & 1;
         if (!mbarrier_wait(&v.full[s], phase, &g_status, STATUS_WAIT_FULL | 0x5000 | s, MMA_BACKOFF_NS)) break;
         if (!mbarrier_wait(&dot_empty[buffer], buffer_phase ^ 1, &g_status, STATUS_WAIT_TMEM_EMPTY | 0x5000 | buffer, MMA_BACKOFF_NS)) break;
         tcgen05_fence_after();
-        const uint32_t a_address = smem_u32(v.tile_a + s * A_BYTES + half * A_HALF_BYTES) + gl * 64;
-        const uint32_t b_address = smem_u32(v.tile_b + s * B_BYTES + half * B_HALF_BYTES + team * (B_BOX_ROWS * 128)) + gl * 64;
+        const uint32_t a_address = smem_u32(v.tile_a + s * A_BYTES + half * A_HALF_BYTES);
+        const uint32_t b_address = smem_u32(v.tile_b + s * B_BYTES + half * B_HALF_BYTES + team * (B_BOX_ROWS * 128));
+        const uint32_t accumulator = v.tmem_base + (team * BUFFERS + buffer) * BUFFER_COLUMNS;
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk)
-            umma_f8_pair(v.tmem_base + (team * BUFFERS + buffer) * TEAM_COLUMNS, umma_desc_k_sw128(a_address + kk * 32),
-                         umma_desc_k_sw128(b_address + kk * 32), idesc, kk);
+        for (int gl = 0; gl < 2; ++gl)
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk)
+                umma_f8_pair(accumulator + gl * TEAM_COLUMNS, umma_desc_k_sw128(a_address + gl * 64 + kk * 32),
+                             umma_desc_k_sw128(b_address + gl * 64 + kk * 32), idesc, kk);
         tcgen05_commit_pair(&dot_full[buffer]);
     }
 }
 
 // Warps 8-23: a warp folds 32 rows x 32 columns of this CTA's half of the tile; a thread owns one
 // row (its TMEM lane) and 32 accumulators.
-// Per group a warp waits for the dots, starts the copy of its 32 x 32 of them into registers (one
+// Per slab a warp looks at the barrier once; per group it starts the copy of its 32 x 32 dots into registers (one
 // tcgen05.ld.32x32b.x32, the shape with the highest TMEM read rate), computes the scale products
-// of its first HOIST columns meanwhile, hands the buffer back once the copy has landed and then
-// does the arithmetic; the other three warps of its scheduler fill the waits.
+// of its first HOIST columns meanwhile and does the arithmetic once the copy has landed; the buffer goes back
+// when the copy of the slab's second group has landed. The other three warps of its scheduler fill the waits.
 // All lanes need the same weight scales: one 16-byte broadcast load per four columns.
 // The arithmetic is the packed fp32 pair form of  acc = fma(dot, sa * sw, acc): each half is
 // IEEE-rounded exactly like the scalar instruction, so the result has the reference's bits.
@@ -324,12 +334,15 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
     const int quadrant = warp & 3, slice = (warp - FOLD_WARP0) >> 2, team = slice / (TEAM_COLUMNS / COLUMNS);
     const uint32_t dot_full = smem_u32(v.dot_full + team * BUFFERS);
     const uint32_t leader_dot_empty = map_to_cta(smem_u32(v.dot_empty + team * BUFFERS), 0);
-    const uint32_t tmem_lane = v.tmem_base + team * BUFFERS * TEAM_COLUMNS + (slice % (TEAM_COLUMNS / COLUMNS)) * COLUMNS +
+    const uint32_t tmem_lane = v.tmem_base + team * BUFFERS * BUFFER_COLUMNS + (slice % (TEAM_COLUMNS / COLUMNS)) * COLUMNS +
                                (static_cast<uint32_t>(quadrant * 32) << 16);
     const uint32_t sw_base = smem_u32(v.sw_tile) + slice * COLUMNS * 4;
     const uint32_t sa_base = smem_u32(v.sa_tile) + (quadrant * 32 + lane) * 16;
     const uint32_t scale_ready = smem_u32(v.scale_ready), empty = smem_u32(v.empty);
     uint32_t dots[COLUMNS];  // dots[j] = dot of this thread's row and column j of the warp's 32
+    // A look at a barrier is one try_wait by every lane; a lane that finds the phase incomplete polls on its own, with
+    // pauses (the fold warps are the pace-setters: that path is for the first groups and for errors). A wait that ran
+    // out of time sets `failed` in its lane; the warp looks at the flags once per stage.
     bool alive = true, failed = false;
     uint32_t s = 0, phase = 0, group_count = 0;
     for (int tile = v.pair; tile < v.tiles && alive; tile += v.pairs) {
@@ -340,15 +353,20 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
         for (int j = 0; j < COLUMNS / 2; ++j) acc[j] = 0;
         for (int ks = 0; ks < v.k_stages && alive; ++ks) {
             if (__any_sync(0xffffffffu, failed)) { alive = false; break; }
-            failed = !wait_warp_u32(scale_ready + s * 8, phase, STATUS_WAIT_READY | 0x5000 | s, lane, FOLD_BACKOFF_NS);
+            failed = false;
+            if (!try_wait_u32(scale_ready + s * 8, phase)) failed = !wait_slow_u32(scale_ready + s * 8, phase, STATUS_WAIT_READY | 0x5000 | s, FOLD_BACKOFF_NS);
+            __syncwarp();
             const uint32_t sw_stage = sw_base + s * SW_BYTES;
 #pragma unroll
             for (int gl = 0; gl < STAGE_GROUPS; ++gl, ++group_count) {
-                const uint32_t buffer = group_count % BUFFERS;
-                failed |= !wait_warp_u32(dot_full + buffer * 8, (group_count / BUFFERS) & 1,
-                                         STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, lane, FOLD_BACKOFF_NS);
-                tcgen05_fence_after();
-                tmem_load_32x32(tmem_lane + buffer * TEAM_COLUMNS, dots);
+                const uint32_t slab = group_count >> 1, buffer = slab % BUFFERS, slab_parity = (slab / BUFFERS) & 1;
+                if ((gl & 1) == 0) {
+                    if (!try_wait_u32(dot_full + buffer * 8, slab_parity))
+                        failed |= !wait_slow_u32(dot_full + buffer * 8, slab_parity, STATUS_WAIT_TMEM_FULL | 0x5000 | buffer, FOLD_BACKOFF_NS);
+                    __syncwarp();
+                    tcgen05_fence_after();
+                }
+                tmem_load_32x32(tmem_lane + buffer * BUFFER_COLUMNS + (gl & 1) * TEAM_COLUMNS, dots);
                 // while the copy is in flight: the scale products of the first HOIST columns
                 const float scale = lds_f32(sa_base + s * SA_BYTES + gl * 4);
                 const uint64_t sa2 = pack_f32x2(scale, scale);
@@ -362,9 +380,11 @@ __device__ __forceinline__ void fold_role(const View &v, const float *__restrict
                     p[2 * q + 1] = mul_f32x2(sa2, sw4.y);
                 }
                 tmem_load_wait_32(dots);
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbarrier_arrive_cluster(leader_dot_empty + buffer * 8);
+                if ((gl & 1) == 1) {  // both groups of the slab are in registers or folded: hand the buffer back
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbarrier_arrive_cluster(leader_dot_empty + buffer * 8);
+                }
                 if (DUMP_DOTS && row < shape.m) {
 #pragma unroll
                     for (int j = 0; j < COLUMNS; ++j)
@@ -511,7 +531,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         fence_barrier_init();
     }
     if (warp == MMA_WARP0) {
-        tmem_alloc_pair(tmem_slot, TEAMS * BUFFERS * TEAM_COLUMNS);
+        tmem_alloc_pair(tmem_slot, TEAMS * BUFFERS * BUFFER_COLUMNS);
         tmem_relinquish_pair();
     }
     tcgen05_fence_before();
@@ -548,7 +568,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (warp == MMA_WARP0) {
         __syncwarp();
         tcgen05_fence_after();
-        tmem_dealloc_pair(tmem_base, TEAMS * BUFFERS * TEAM_COLUMNS);
+        tmem_dealloc_pair(tmem_base, TEAMS * BUFFERS * BUFFER_COLUMNS);
     }
 }
 
