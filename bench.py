@@ -57,7 +57,7 @@ CPU_PASSES = 5
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one w4a4_pair::gemm_kernel launch on the qkv
 # shape at M = 4096, whose 2MNK is the average of the block's four launches: from the ncu capture that the
 # kernel's profile summary records. Scaled by rows and ranks for other workloads; None for other kernels.
-NCU_TRAFFIC_BYTES_QKV_M4096 = 78.4e6
+NCU_TRAFFIC_BYTES_QKV_M4096 = 82.7e6
 
 
 def block_ops(m: int) -> float:
