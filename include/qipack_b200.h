@@ -103,13 +103,16 @@ int qi_w4a4_gemm_noalloc_ex(const void *a_codes, const void *a_scales, const voi
  * the same bits): 0 = by shape; 1 = the int8 kernel that widens the nibbles in shared memory (any k % 128 == 0);
  * 2 = both operands widened to one byte per code in scratch memory, then the byte-operand kernel on CTA pairs
  * (k % 256 == 0, scale arrays 8-byte aligned). Path 2, and path 0 where it chooses path 2 (m, n >= 256 and the
- * conditions of path 2), take (m + n) * k bytes from the device's memory pool with cudaMallocAsync and give them
- * back with cudaFreeAsync, both in stream order; when the pool refuses, path 0 runs path 1 instead. A caller that
+ * conditions of path 2), take (m + n) * k bytes from a memory pool of the library's own (one per device, made at
+ * first use, cudaMallocFromPoolAsync) and give them back with cudaFreeAsync, both in stream order; the pool keeps
+ * the memory for the next call until qi_w4a4_scratch_trim() returns what is unused to the system. When the pool
+ * refuses, path 0 runs path 1 instead. A caller that
  * holds the weights for many calls widens them once (qi_w4a4_widen_codes_ex) and calls qi_w4a4_gemm_wide_ex.
  * No counterpart in the reference (gemm.cu:65-189 is one kernel). */
 int qi_w4a4_gemm_path_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,
                          const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, int path,
                          void *stream);
+int qi_w4a4_scratch_trim(void);
 
 /* qi_f32_to_f16 on a stream. */
 int qi_f32_to_f16_ex(const float *source, void *out, unsigned long long count, void *stream);

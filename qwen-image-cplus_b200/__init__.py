@@ -92,6 +92,7 @@ SIGNATURES = {
     "qi_w4a4_quantize_activations_ex": [_P, _I, _P, _P, _I, _I, _P],
     "qi_w4a4_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
     "qi_w4a4_gemm_path_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _P],
+    "qi_w4a4_scratch_trim": [],
     "qi_w4a4_gemm_noalloc_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
     "qi_w4a16_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
     "qi_w4a16_gemv_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
@@ -208,6 +209,11 @@ def w4a4_gemm_ex(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype: int, ld
 
 W4A4_PATH_BY_SHAPE, W4A4_PATH_INT8, W4A4_PATH_WIDENED = 0, 1, 2
 NOALLOC_SCRATCH_BYTES, NOALLOC_TOO_LARGE = 64 << 20, 30001
+
+
+def w4a4_scratch_trim() -> int:
+    """Returns the unused memory of the current device's scratch pool of the packed W4A4 entry points to the system."""
+    return lib().qi_w4a4_scratch_trim()
 
 
 def w4a4_gemm_noalloc_ex(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype: int, ldy: int, m: int, n: int, k: int,

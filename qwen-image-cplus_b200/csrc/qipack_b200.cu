@@ -337,9 +337,36 @@ int w4a4_gemm_wide(const void *a_bytes, const void *a_scales, const void *w_byte
 // nibbles in shared memory; 2 = both operands widened to one byte per code in scratch memory of the stream's pool
 // (two small kernels), then the byte-operand kernel on CTA pairs, which is the faster GEMM by more than the
 // widening costs once the matrices are large; 0 = 2 where the pair kernel takes the shape, else 1. Same bits on
-// every path. The scratch is (m + n) * k bytes from cudaMallocAsync and goes back with cudaFreeAsync, both in
-// stream order; if the pool refuses, path 0 falls back to 1.
+// every path. The scratch is (m + n) * k bytes from the library's own memory pool (cudaMallocFromPoolAsync) and goes
+// back with cudaFreeAsync, both in stream order; if the pool refuses, path 0 falls back to 1.
 constexpr int W4A4_PATHS = 3;
+
+// The library's own memory pool for that scratch, one per device, made at first use. The device's default pool gives
+// its memory back to the system at every synchronisation (release threshold 0), so a caller that synchronises
+// between calls would pay a round trip to the driver per call (measured: 1.0-1.7 ms instead of 0.32 ms for the
+// 4096 x 9216 x 3072 linear); this pool keeps what it has handed out until qi_w4a4_scratch_trim.
+cudaMemPool_t scratch_pool(int device) {
+    static std::atomic<cudaMemPool_t> pools[MAX_DEVICES];
+    cudaMemPool_t pool = pools[device].load(std::memory_order_acquire);
+    if (pool != nullptr) return pool;
+    cudaMemPoolProps properties = {};
+    properties.allocType = cudaMemAllocationTypePinned;
+    properties.handleTypes = cudaMemHandleTypeNone;
+    properties.location.type = cudaMemLocationTypeDevice;
+    properties.location.id = device;
+    if (cudaMemPoolCreate(&pool, &properties) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    unsigned long long keep = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    cudaMemPool_t expected = nullptr;
+    if (!pools[device].compare_exchange_strong(expected, pool, std::memory_order_acq_rel)) {
+        cudaMemPoolDestroy(pool);  // another host thread was first
+        pool = expected;
+    }
+    return pool;
+}
 int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales, const float *bias,
               void *y, int y_dtype, long long ldy, int32_t *dots, int m, int n, int k, int path, cudaStream_t stream) {
     if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 128 != 0 || path < 0 || path >= W4A4_PATHS) return INVALID;
@@ -357,7 +384,9 @@ int w4a4_gemm(const void *a_codes, const void *a_scales, const void *w_codes, co
         const size_t a_bytes = (static_cast<size_t>(m) * k + 255) & ~static_cast<size_t>(255);
         const size_t w_bytes = static_cast<size_t>(n) * k;
         uint8_t *scratch = nullptr;
-        const cudaError_t allocated = cudaMallocAsync(reinterpret_cast<void **>(&scratch), a_bytes + w_bytes, stream);
+        const cudaMemPool_t pool = scratch_pool(device);
+        const cudaError_t allocated = pool == nullptr ? cudaErrorMemoryAllocation
+                                                      : cudaMallocFromPoolAsync(reinterpret_cast<void **>(&scratch), a_bytes + w_bytes, pool, stream);
         if (allocated == cudaSuccess) {
             int status = qi_w4a4_widen_codes_ex(a_codes, scratch, m, k, stream);
             if (status == 0) status = qi_w4a4_widen_codes_ex(w_codes, scratch + a_bytes, n, k, stream);
@@ -493,6 +522,14 @@ int qi_w4a4_gemm_ex(const void *a_codes, const void *a_scales, const void *w_cod
                     const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
     return w4a4_gemm(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype, ldy, nullptr, m, n, k, 0,
                      static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a4_scratch_trim(void) {
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    const cudaMemPool_t pool = scratch_pool(device);
+    if (pool == nullptr) return static_cast<int>(cudaErrorMemoryAllocation);
+    return static_cast<int>(cudaMemPoolTrimTo(pool, 0));
 }
 
 int qi_w4a4_gemm_path_ex(const void *a_codes, const void *a_scales, const void *w_codes, const void *w_scales,

@@ -360,7 +360,12 @@ def test_w4a4_gemm_paths_give_the_same_bits(qi, m, n, k):
         assert qi.w4a4_gemm_path_ex(*args, y, qi.DTYPE_F32, n, m, n, k, path) == 0
         check_status(qi)
         assert np.array_equal(y.cpu().numpy(), expected), path
+    torch.cuda.synchronize()
+    assert qi.w4a4_scratch_trim() == 0  # the pool gives back what no call holds; the next call takes it again
     y = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+    assert qi.w4a4_gemm_path_ex(*args, y, qi.DTYPE_F32, n, m, n, k, qi.W4A4_PATH_BY_SHAPE) == 0
+    check_status(qi)
+    assert np.array_equal(y.cpu().numpy(), expected)
     assert qi.w4a4_gemm_path_ex(*args, y, qi.DTYPE_F32, n, m, n, k, 3) == qi.CUDA_ERROR_INVALID_VALUE
     if k % 256 != 0:  # the pair kernel's stage is four groups
         assert qi.w4a4_gemm_path_ex(*args, y, qi.DTYPE_F32, n, m, n, k, qi.W4A4_PATH_WIDENED) == qi.CUDA_ERROR_INVALID_VALUE
