@@ -265,7 +265,17 @@ def other_kernels(qi, torch, device, stream, peaks, tensor_peaks, m):
     out["w4a16_gemv"] = {"n": n, "k": k, "us": ms * 1e3, "bytes": gemv_bytes,
                          "roofline": {"bound": "hbm", "achieved": gemv_bytes / ms / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                       "frac": gemv_bytes / ms / 1e6 / peaks["hbm_gbs"]}}
-    del copies
+    # the grouped form: sixteen matrices per launch (none of them in L2 at its turn: 510 MB per launch)
+    group_copies = copies + [make_packed_w4a16(torch, generator, n, k, device) for _ in range(8)]
+    group_outputs = [torch.empty(1, n, dtype=torch.float16, device=device) for _ in group_copies]
+    table, keep = qi.gemv_items([(c, s_, m_, None, out_) for (c, s_, m_), out_ in zip(group_copies, group_outputs)])
+    ms = graph_timed(torch, stream, lambda i: qi.w4a16_gemv_grouped_ex(x1, table, qi.DTYPE_F16, n, 1, n, k, handle), 6)
+    per_matrix_ms = ms / len(group_copies)
+    out["w4a16_gemv_grouped"] = {"n": n, "k": k, "matrices_per_launch": len(group_copies), "us_per_matrix": per_matrix_ms * 1e3,
+                                 "bytes_per_matrix": gemv_bytes,
+                                 "roofline": {"bound": "hbm", "achieved": gemv_bytes / per_matrix_ms / 1e6, "peak": peaks["hbm_gbs"],
+                                              "unit": "GB/s", "frac": gemv_bytes / per_matrix_ms / 1e6 / peaks["hbm_gbs"]}}
+    del copies, group_copies, group_outputs, table, keep
 
     out["quantiser"] = []
     for k in (3072, 12288):
@@ -1021,11 +1031,18 @@ def run_stack(args):
                                    torch.empty(rows * k_max, dtype=torch.float16, device=device),
                                    wide=torch.empty(rows * k_max, dtype=torch.uint8, device=device)))
     gemv_x = make_activations(torch, generator, 1, GEMV_K, "silu", device)
-    gemv_y = torch.empty(1, GEMV_N, dtype=torch.float16, device=device)
+    # every block's modulation linears read the same conditioning vector: one grouped launch per 64 matrices at the
+    # start of the step instead of one launch per matrix inside its block
+    gemv_table = gemv_keep = None
+    if gemv_records:
+        gemv_table, gemv_keep = qi.gemv_items([(codes, scales, minimums, None, torch.empty(1, GEMV_N, dtype=torch.float16, device=device))
+                                               for codes, scales, minimums in gemv_records])
     launches = {"count": 0}
 
     def step():
-        gemv_index = 0
+        if gemv_table is not None:  # replicated on every rank: 32 MB of weights each
+            assert qi.w4a16_gemv_grouped_ex(gemv_x, gemv_table, qi.DTYPE_F16, GEMV_N, 1, GEMV_N, GEMV_K, handle) == 0
+            launches["count"] += (len(gemv_table) + 63) // 64
         for position, (record, stream_index, linear_index) in enumerate(plan):
             rows = streams[stream_index][1]
             x, y = inputs[stream_index][linear_index], outputs[stream_index][linear_index]
@@ -1037,12 +1054,6 @@ def run_stack(args):
                                         input_dtype=qi.DTYPE_F16, output_dtype=qi.DTYPE_F16, stream=handle)
             assert status == 0, f"linear {position}: status {status}"
             launches["count"] += 2 if record.scheme == qi.SCHEME_W4A4_H256 else 1
-            if gemvs_per_block and (position + 1) % (len(streams) * len(LINEARS)) == 0:
-                for _ in range(gemvs_per_block):  # replicated on every rank: 32 MB of weights each
-                    codes, scales, minimums = gemv_records[gemv_index]
-                    assert qi.w4a16_gemv_ex(gemv_x, codes, scales, minimums, None, gemv_y, qi.DTYPE_F16, GEMV_N, 1, GEMV_N, GEMV_K, handle) == 0
-                    gemv_index += 1
-                    launches["count"] += 1
 
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
@@ -1113,7 +1124,7 @@ def run_stack(args):
             "dtype": "fp16 x int4 (W4A16) and int4 x int4 (W4A4) packed linears, fp32 accumulate",
             "data": "synthetic: random valid QIPACK v6 records, X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2: GELU-tanh); seed 4242",
             "config": {"workload": ("60-block W4A16 g64 linear stack of one denoising step: image M=4096 + text M=256, two M=1 "
-                                    "modulation GEMVs 3072->18432 per block" if args.workload == "c3" else
+                                    "modulation GEMVs 3072->18432 per block (all of a step's in one grouped launch per 64)" if args.workload == "c3" else
                                     "image-edit stack: rows 2 x (12288 + 512), 60 blocks x 4 linears, each W4A4 with probability 0.7 else W4A16 (seeded)"),
                        "name": args.workload, "blocks": blocks, "ops_per_step": ops,
                        "gemv_bytes_per_step": gemv_bytes * gemvs_per_block * blocks,

@@ -128,6 +128,21 @@ int qi_w4a16_gemm_ex(const void *x_half, const void *codes, const void *scales, 
 int qi_w4a16_gemv_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
                      const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream);
 
+/* `count` matrices of one shape [n, k] against the SAME activations x [m, k], 1 <= m <= 8, in one launch per 64
+ * matrices: item i writes y_i [m, ldy] = x . W_i^T (+ bias_i). For the adaLN modulation linears of a denoising step:
+ * every block has its own weights and all of them read the same conditioning vector, so the 2 x 60 launches of a
+ * step become two (the launch, the first copies and the staging of x are paid once; the weights stream through as
+ * one list of tiles). `items` is host memory, read during the call. n % 16 == 0, k % 64 == 0, k <= 4096; codes,
+ * scales and minimums of every item 16-byte aligned. Same bits as qi_w4a16_gemv_ex. No counterpart in the reference
+ * (its modulation linear is one BF16 cuBLAS call per block, transformer.cplus:716-730). */
+typedef struct qi_gemv_item {
+    const void *codes, *scales, *minimums; /* [n, k/2] uint8, [n, k/64] float16 each */
+    const float *bias;                     /* [n] or NULL */
+    void *y;                               /* [m, ldy] of y_dtype */
+} qi_gemv_item;
+int qi_w4a16_gemv_grouped_ex(const void *x_half, const qi_gemv_item *items, int count, int y_dtype, long long ldy,
+                             int m, int n, int k, void *stream);
+
 /* As qi_w4a16_gemm_ex with the tile chosen by the caller instead of by shape (for tests and
  * tuning; every tile gives results within the operator's tolerance, not the same bits):
  * 0 = by shape, 1 = 128x128, 2 = 256x128, 3 = 128x256, 4 = 256x256, 5 = 256x256 on a CTA pair.

@@ -54,6 +54,11 @@ class qi_packed_linear(ctypes.Structure):
                 ("zeros", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("weights_wide", ctypes.c_void_p)]
 
 
+class qi_gemv_item(ctypes.Structure):
+    _fields_ = [("codes", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("minimums", ctypes.c_void_p),
+                ("bias", ctypes.c_void_p), ("y", ctypes.c_void_p)]
+
+
 class qi_linear_work(ctypes.Structure):
     _fields_ = [("codes", ctypes.c_void_p), ("code_scales", ctypes.c_void_p), ("halves", ctypes.c_void_p),
                 ("wide", ctypes.c_void_p)]
@@ -91,6 +96,7 @@ SIGNATURES = {
     "qi_f32_to_f16_ex": [_P, _P, _ULL, _P],
     "qi_w4a4_quantize_activations_ex": [_P, _I, _P, _P, _I, _I, _P],
     "qi_w4a4_gemm_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
+    "qi_w4a16_gemv_grouped_ex": [_P, ctypes.POINTER(qi_gemv_item), _I, _I, _LL, _I, _I, _I, _P],
     "qi_w4a4_gemm_path_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _P],
     "qi_w4a4_scratch_trim": [],
     "qi_w4a4_gemm_noalloc_ex": [_P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _P],
@@ -205,6 +211,21 @@ def w4a4_gemm_ex(a_codes, a_scales, w_codes, w_scales, bias, y, y_dtype: int, ld
                  stream=None) -> int:
     return lib().qi_w4a4_gemm_ex(_p(a_codes), _p(a_scales), _p(w_codes), _p(w_scales), _p(bias), _p(y), y_dtype,
                                  ldy, m, n, k, _p(stream))
+
+
+def gemv_items(entries):
+    """A host table for w4a16_gemv_grouped_ex from (codes, scales, minimums, bias or None, y) tuples of device tensors.
+    Returns (table, keep): `keep` holds the tensors so that they outlive the table."""
+    table = (qi_gemv_item * len(entries))()
+    for slot, (codes, scales, minimums, bias, y) in zip(table, entries):
+        slot.codes, slot.scales, slot.minimums = _p(codes), _p(scales), _p(minimums)
+        slot.bias, slot.y = (_p(bias) if bias is not None else None), _p(y)
+    return table, list(entries)
+
+
+def w4a16_gemv_grouped_ex(x_half, table, y_dtype: int, ldy: int, m: int, n: int, k: int, stream=None) -> int:
+    """len(table) matrices [n, k] against the same x [m, k] in one launch per 64 (table from gemv_items)."""
+    return lib().qi_w4a16_gemv_grouped_ex(_p(x_half), table, len(table), y_dtype, ldy, m, n, k, _p(stream))
 
 
 W4A4_PATH_BY_SHAPE, W4A4_PATH_INT8, W4A4_PATH_WIDENED = 0, 1, 2

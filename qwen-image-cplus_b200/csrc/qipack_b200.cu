@@ -280,6 +280,46 @@ int w4a16_gemv(const void *x_half, const void *codes, const void *scales, const 
     return static_cast<int>(cudaGetLastError());
 }
 
+// Several matrices of one shape against the same activations: launches of up to STREAM_GROUP matrices each.
+int w4a16_gemv_grouped(const void *x_half, const qi_gemv_item *items, int count, int y_dtype, long long ldy, int m, int n,
+                       int k, cudaStream_t stream) {
+    if (m < 1 || m > 8 || n <= 0 || k <= 0 || n % 16 != 0 || k % 64 != 0 || count < 1 || items == nullptr) return INVALID;
+    if (!x_half || !aligned16(x_half) || k > w4a16::STREAM_MAX_K) return INVALID;
+    if (ldy < n || (y_dtype != QI_DTYPE_F32 && y_dtype != QI_DTYPE_F16)) return INVALID;
+    for (int i = 0; i < count; ++i) {
+        const qi_gemv_item &item = items[i];
+        if (!item.codes || !item.scales || !item.minimums || !item.y) return INVALID;
+        if (!aligned16(item.codes) || !aligned16(item.scales) || !aligned16(item.minimums)) return INVALID;
+    }
+    const int device = current_device();
+    if (device < 0) return INVALID;
+    constexpr int CTA_BYTES = 110 * 1024;  // two CTAs per SM, as for the single matrix
+    int stages = (CTA_BYTES - 128 - w4a16::stream_x_bytes(m, k)) / w4a16::stream_stage_bytes(k);
+    stages = stages > w4a16::STREAM_MAX_STAGES ? w4a16::STREAM_MAX_STAGES : stages;
+    if (stages < 1) return INVALID;
+    static std::atomic<bool> configured[MAX_DEVICES];
+    if (const cudaError_t error = configure_once(w4a16::gemv_stream_grouped_kernel, CTA_BYTES, configured[device]))
+        return static_cast<int>(error);
+    const int smem_bytes = stages * w4a16::stream_stage_bytes(k) + w4a16::stream_x_bytes(m, k) + 128;
+    const int resident = 2 * sm_count(device);
+    for (int first = 0; first < count; first += w4a16::STREAM_GROUP) {
+        const int now = count - first < w4a16::STREAM_GROUP ? count - first : w4a16::STREAM_GROUP;
+        w4a16::StreamItems group;
+        for (int i = 0; i < now; ++i) {
+            const qi_gemv_item &item = items[first + i];
+            group.item[i] = {static_cast<const uint8_t *>(item.codes), static_cast<const __half *>(item.scales),
+                             static_cast<const __half *>(item.minimums), item.bias, item.y};
+        }
+        for (int i = now; i < w4a16::STREAM_GROUP; ++i) group.item[i] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+        const long long tiles = static_cast<long long>(now) * (n / w4a16::STREAM_ROWS);
+        w4a16::gemv_stream_grouped_kernel<<<tiles < resident ? static_cast<int>(tiles) : resident, w4a16::STREAM_THREADS, smem_bytes, stream>>>(
+            static_cast<const __half *>(x_half), group, now, m, n, k, ldy, y_dtype == QI_DTYPE_F16, stages);
+        const cudaError_t launched = cudaGetLastError();
+        if (launched != cudaSuccess) return static_cast<int>(launched);
+    }
+    return 0;
+}
+
 int w4a16_gemm(const void *x_half, const void *codes, const void *scales, const void *minimums, const float *bias,
                void *y, int y_dtype, long long ldy, int m, int n, int k, int tile, cudaStream_t stream) {
     if (m <= 0 || n <= 0 || k <= 0 || n % 32 != 0 || k % 64 != 0) return INVALID;
@@ -596,6 +636,11 @@ int qi_w4a4_group_dots_ex(const void *a_codes, const void *a_scales, const void 
 int qi_w4a16_gemv_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,
                      const float *bias, void *y, int y_dtype, long long ldy, int m, int n, int k, void *stream) {
     return w4a16_gemv(x_half, codes, scales, minimums, bias, y, y_dtype, ldy, m, n, k, static_cast<cudaStream_t>(stream));
+}
+
+int qi_w4a16_gemv_grouped_ex(const void *x_half, const qi_gemv_item *items, int count, int y_dtype, long long ldy, int m,
+                             int n, int k, void *stream) {
+    return w4a16_gemv_grouped(x_half, items, count, y_dtype, ldy, m, n, k, static_cast<cudaStream_t>(stream));
 }
 
 int qi_w4a16_gemm_ex(const void *x_half, const void *codes, const void *scales, const void *minimums,

@@ -63,11 +63,27 @@ __device__ __forceinline__ void unpack_word_any_scale(uint32_t word, __half2 sca
     }
 }
 
+// Several matrices of one shape for one launch: the grouped form walks the tiles of all of them as one list, so
+// that the launch, the first copies and the staging of the activations are paid once. The table travels in the
+// kernel's parameters (40 bytes per matrix).
+constexpr int STREAM_GROUP = 64;
+struct StreamItem {
+    const uint8_t *codes;
+    const __half *scales, *minimums;
+    const float *bias;
+    void *y;
+};
+struct StreamItems {
+    StreamItem item[STREAM_GROUP];
+};
+
 // Dynamic shared memory: `stages` stages of stream_stage_bytes(k), then the activations (m * k * 2 bytes).
-__global__ void __launch_bounds__(STREAM_THREADS, 2)
-gemv_stream_kernel(const __half *__restrict__ x, const uint8_t *__restrict__ codes, const __half *__restrict__ scales,
+// GROUPED: `count` matrices [n, k] from `group`, tile t of the launch is tile t % (n / 16) of matrix t / (n / 16);
+// otherwise the one matrix given by the pointer arguments.
+template <bool GROUPED>
+__device__ __forceinline__ void gemv_stream_body(const __half *__restrict__ x, const uint8_t *__restrict__ codes, const __half *__restrict__ scales,
                    const __half *__restrict__ minimums, const float *__restrict__ bias, void *__restrict__ y,
-                   int m, int n, int k, long long ldy, int y_is_half, int stages) {
+                   int m, int n, int k, long long ldy, int y_is_half, int stages, const StreamItems *group, int count) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     __shared__ uint64_t full[STREAM_MAX_STAGES];
@@ -77,7 +93,7 @@ gemv_stream_kernel(const __half *__restrict__ x, const uint8_t *__restrict__ cod
     const int groups = k / 64, steps = (groups + 1) / 2;  // a step: two groups, a quarter of the lanes on each half group
     const int code_bytes = STREAM_ROWS * (k / 2), scale_bytes = STREAM_ROWS * groups * 2;
     const int stage_bytes = code_bytes + 2 * scale_bytes;
-    const int tiles = n / STREAM_ROWS;
+    const int tiles_each = n / STREAM_ROWS, tiles = GROUPED ? tiles_each * count : tiles_each;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) mbarrier_init(&full[s], 1);
@@ -93,11 +109,18 @@ gemv_stream_kernel(const __half *__restrict__ x, const uint8_t *__restrict__ cod
     __syncthreads();
     auto fetch = [&](int tile, int s) {  // thread 0 only
         uint8_t *stage = smem + static_cast<size_t>(s) * stage_bytes;
+        const uint8_t *from_codes = codes;
+        const __half *from_scales = scales, *from_minimums = minimums;
+        if (GROUPED) {
+            const StreamItem &item = group->item[tile / tiles_each];
+            from_codes = item.codes, from_scales = item.scales, from_minimums = item.minimums;
+            tile %= tiles_each;
+        }
         const size_t row0 = static_cast<size_t>(tile) * STREAM_ROWS;
         mbarrier_arrive_expect_tx(&full[s], static_cast<uint32_t>(stage_bytes));
-        bulk_load(stage, codes + row0 * (k / 2), code_bytes, &full[s]);
-        bulk_load(stage + code_bytes, scales + row0 * groups, scale_bytes, &full[s]);
-        bulk_load(stage + code_bytes + scale_bytes, minimums + row0 * groups, scale_bytes, &full[s]);
+        bulk_load(stage, from_codes + row0 * (k / 2), code_bytes, &full[s]);
+        bulk_load(stage + code_bytes, from_scales + row0 * groups, scale_bytes, &full[s]);
+        bulk_load(stage + code_bytes + scale_bytes, from_minimums + row0 * groups, scale_bytes, &full[s]);
     };
     if (threadIdx.x == 0) {
         int tile = blockIdx.x;
@@ -170,19 +193,40 @@ gemv_stream_kernel(const __half *__restrict__ x, const uint8_t *__restrict__ cod
         }
         if (threadIdx.x < 16 * 8) {  // fixed-order sum over the K slices: thread -> (weight row, activation row)
             const int row = threadIdx.x >> 3, b = threadIdx.x & 7;
-            const int out_row = tile * STREAM_ROWS + row;
+            const float *to_bias = bias;
+            void *to_y = y;
+            int local_tile = tile;
+            if (GROUPED) {
+                const StreamItem &item = group->item[tile / tiles_each];
+                to_bias = item.bias, to_y = item.y;
+                local_tile = tile % tiles_each;
+            }
+            const int out_row = local_tile * STREAM_ROWS + row;
             if (b < m) {
                 float total = 0.0f;
 #pragma unroll
                 for (int slice = 0; slice < STREAM_WARPS; ++slice) total += partial[slice][row][b];
-                if (bias != nullptr) total += __ldg(bias + out_row);
-                if (y_is_half) static_cast<__half *>(y)[static_cast<size_t>(b) * ldy + out_row] = __float2half_rn(total);
-                else static_cast<float *>(y)[static_cast<size_t>(b) * ldy + out_row] = total;
+                if (to_bias != nullptr) total += __ldg(to_bias + out_row);
+                if (y_is_half) static_cast<__half *>(to_y)[static_cast<size_t>(b) * ldy + out_row] = __float2half_rn(total);
+                else static_cast<float *>(to_y)[static_cast<size_t>(b) * ldy + out_row] = total;
             }
         }
         __syncthreads();  // the partial sums have been read before the next tile overwrites them
         if (++s == static_cast<uint32_t>(stages)) s = 0, phase ^= 1;
     }
+}
+
+__global__ void __launch_bounds__(STREAM_THREADS, 2)
+gemv_stream_kernel(const __half *__restrict__ x, const uint8_t *__restrict__ codes, const __half *__restrict__ scales,
+                   const __half *__restrict__ minimums, const float *__restrict__ bias, void *__restrict__ y,
+                   int m, int n, int k, long long ldy, int y_is_half, int stages) {
+    gemv_stream_body<false>(x, codes, scales, minimums, bias, y, m, n, k, ldy, y_is_half, stages, nullptr, 1);
+}
+
+__global__ void __launch_bounds__(STREAM_THREADS, 2)
+gemv_stream_grouped_kernel(const __half *__restrict__ x, const __grid_constant__ StreamItems group, int count,
+                           int m, int n, int k, long long ldy, int y_is_half, int stages) {
+    gemv_stream_body<true>(x, nullptr, nullptr, nullptr, nullptr, nullptr, m, n, k, ldy, y_is_half, stages, &group, count);
 }
 
 }  // namespace w4a16

@@ -259,6 +259,40 @@ def test_w4a16_gemv_scales_of_every_size(qi, m):
     assert qt.max_relative_error(y.cpu().numpy(), expected) <= OUTPUT_TOLERANCE
 
 
+@pytest.mark.parametrize("m,count,n,k", [(1, 3, 1024, 1216), (1, 70, 256, 512), (2, 5, 18432, 3072)])
+def test_w4a16_gemv_grouped_matches_oracle_and_the_single_launches(qi, m, count, n, k):
+    """Several matrices of one shape against the same activations in one launch (two for more than 64 matrices): every
+    output equals the oracle's within the tolerance and the single-matrix GEMV's bit for bit."""
+    rng = np.random.default_rng(3200 + m + count + n + k)
+    x16 = qt.make_activations(rng, m, k, "silu")
+    x = up(x16)
+    entries, singles, expected = [], [], []
+    for index in range(count):
+        codes, scales, minimums = qt.random_w4a16_pack(rng, n, k)
+        bias = qt.make_bias(rng, n) if index % 2 == 0 else None
+        device = (up(codes), up(scales), up(minimums), up(bias) if bias is not None else None,
+                  torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda"))
+        entries.append(device)
+        single = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        assert qi.w4a16_gemv_ex(x, device[0], device[1], device[2], device[3], single, qi.DTYPE_F32, n, m, n, k) == 0
+        singles.append(single)
+        if index < 4 or index == count - 1:  # the oracle on a few of them; the single launches cover the rest
+            expected.append((index, qo.w4a16_gemm(x16, codes, scales, minimums, bias=bias)))
+    table, keep = qi.gemv_items(entries)
+    assert qi.w4a16_gemv_grouped_ex(x, table, qi.DTYPE_F32, n, m, n, k) == 0
+    torch.cuda.synchronize()
+    check_status(qi)
+    for index, (entry, single) in enumerate(zip(entries, singles)):
+        assert torch.equal(entry[4], single), index
+    for index, want in expected:
+        assert qt.max_relative_error(entries[index][4].cpu().numpy(), want) <= OUTPUT_TOLERANCE
+    # refused: no items, a misaligned region, rows too long for the streaming kernel
+    assert qi.lib().qi_w4a16_gemv_grouped_ex(qi._p(x), table, 0, qi.DTYPE_F32, n, m, n, k, None) == qi.CUDA_ERROR_INVALID_VALUE
+    bad, _ = qi.gemv_items([(entries[0][0].view(-1)[1:], entries[0][1], entries[0][2], None, entries[0][4])])
+    assert qi.w4a16_gemv_grouped_ex(x, bad, qi.DTYPE_F32, n, m, n, k) == qi.CUDA_ERROR_INVALID_VALUE
+    assert qi.w4a16_gemv_grouped_ex(x, table, qi.DTYPE_F32, n, m, n, 8192) == qi.CUDA_ERROR_INVALID_VALUE
+
+
 # ---- W4A4 ----------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 256), (256, 384, 512), (128, 256, 3072), (384, 128, 1280)])
