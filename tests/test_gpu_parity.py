@@ -624,3 +624,35 @@ def test_a_wait_that_runs_out_reports_its_code_and_leaves_the_device_healthy(qi)
     assert qi.w4a4_gemm(up(a_codes), up(a_scales), up(w_codes), up(w_scales), y, m, n, k) == 0
     check_status(qi)
     assert np.array_equal(y.cpu().numpy(), qo.w4a4_gemm(a_codes, a_scales, w_codes, w_scales))
+
+
+@pytest.mark.parametrize("dtype_name", ["f16", "f32"])
+def test_w4a4_scatter_epilogue_keeps_inside_a_slice_that_ends_within_a_tile(qi, dtype_name):
+    """The GEMM that stores its slice into several copies of the whole output, on one GPU with two local buffers as the
+    copies: n = 160 ends inside the kernel's 128-column tile, so the tile's last 96 columns must not be written. Canary
+    values around the slice, in every copy, stay as they were."""
+    import ctypes
+    rng = np.random.default_rng(8100)
+    m, n, k, ldy, column = 256, 160, 512, 512, 32
+    w_codes, w_scales = qt.random_w4a4_pack(rng, n, k, 1e-3, 6e-3)
+    a_codes, a_scales = qt.random_w4a4_pack(rng, m, k, 0.05, 0.6)
+    expected = qo.w4a4_gemm(a_codes, a_scales, w_codes, w_scales)
+    a_wide = torch.zeros(m, k, dtype=torch.uint8, device="cuda")
+    w_wide = torch.zeros(n, k, dtype=torch.uint8, device="cuda")
+    assert qi.w4a4_widen_codes_ex(up(a_codes), a_wide, m, k) == 0
+    assert qi.w4a4_widen_codes_ex(up(w_codes), w_wide, n, k) == 0
+    dtype, torch_dtype = (qi.DTYPE_F16, torch.float16) if dtype_name == "f16" else (qi.DTYPE_F32, torch.float32)
+    outputs = [torch.full((m, ldy), -3.0, dtype=torch_dtype, device="cuda") for _ in range(2)]
+    copies = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in outputs])
+    assert qi.w4a4_gemm_wide_scatter_ex(a_wide, up(a_scales), w_wide, up(w_scales), None, copies, 1, dtype, ldy, column,
+                                        m, n, k) == 0
+    torch.cuda.synchronize()
+    check_status(qi)
+    for output in outputs:
+        got = output.float().cpu().numpy()
+        assert np.all(got[:, :column] == -3.0) and np.all(got[:, column + n:] == -3.0)
+        if dtype == qi.DTYPE_F32:
+            assert np.array_equal(got[:, column:column + n], expected)
+        else:
+            distance, checked = qt.fp16_store_error(output[:, column:column + n].cpu().numpy(), expected)
+            assert distance <= FP16_STORE_ULPS and checked > 0.5
