@@ -10,11 +10,15 @@
  *     asynchronous errors surface at the caller's next synchronisation;
  *   - all pointers are DEVICE pointers owned by the caller (weights are sub-ranges of one
  *     uploaded pack, so only the pack's 256-byte alignment is assumed; 16 bytes are required);
- *   - the operators allocate nothing and keep no state between calls beyond per-device facts
- *     looked up once (SM count, the kernels' shared-memory opt-in; safe from several host
- *     threads); the device used is the current one; the un-suffixed entry points launch on the
- *     legacy default stream. (The sharding context further down owns a communicator, streams
- *     and events: those are created by qi_shard_create and freed by qi_shard_destroy.)
+ *   - the operators keep no state between calls beyond per-device facts looked up once (SM
+ *     count, the kernels' shared-memory opt-in; safe from several host threads) and allocate
+ *     nothing, with one exception: the W4A4 GEMM on nibble-packed operands (qi_w4a4_gemm,
+ *     qi_w4a4_gemm_ex, and qi_linear on a scheme-6 record without byte-wide weights) takes
+ *     (m + n) * k bytes of scratch per call from a memory pool of the library's own when it
+ *     chooses its widened path (see qi_w4a4_gemm_path_ex; qi_w4a4_gemm_noalloc_ex is the form
+ *     that takes none). The device used is the current one; the un-suffixed entry points launch
+ *     on the legacy default stream. (The sharding context further down owns a communicator,
+ *     streams and events: those are created by qi_shard_create and freed by qi_shard_destroy.)
  *
  * Matrix layouts (row-major):
  *   x        [m, k]     float32 or float16 activations
