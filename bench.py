@@ -520,8 +520,9 @@ def run_block(args):
         if wide_path:
             return qi.w4a4_gemm_wide_ex(layer["a_wide"], layer["a_scales"], layer["w_wide"], layer["w_scales"], None, y_out,
                                         qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
-        return qi.w4a4_gemm_ex(layer["a_codes"], layer["a_scales"], layer["w_codes"], layer["w_scales"], None, y_out,
-                               qi.DTYPE_F16, n_local, m, n_local, k, stream_handle)
+        path = qi.W4A4_PATH_INT8 if args.w4a4_path == "int8" else qi.W4A4_PATH_BY_SHAPE
+        return qi.w4a4_gemm_path_ex(layer["a_codes"], layer["a_scales"], layer["w_codes"], layer["w_scales"], None, y_out,
+                                    qi.DTYPE_F16, n_local, m, n_local, k, path, stream_handle)
 
     def step(index, record_gemm_events=None, slot=None):
         """One pass over the four linears. `slot` selects the end-to-end path's own input/output buffers."""
@@ -680,7 +681,7 @@ def run_block(args):
         e2e_value = ops_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
         # one GPU's GEMM launches: operations of its column slices over the time of its launches
         achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12
-        eight_bit_peak = tensor_peaks["e4m3" if wide_path else "s8"]
+        eight_bit_peak = tensor_peaks["s8" if args.w4a4_path == "int8" else "e4m3"]
         working_set = sum(l["w_wide"].numel() + l["x"].numel() * 2 + l["a_wide"].numel() + l["y_local"].numel() * 2
                           for l in layers)
         if world == 1:
@@ -695,7 +696,7 @@ def run_block(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": ("int4 codes, exact int8 tensor-core group dots, fp32 fold" if not wide_path else
+            "dtype": ("int4 codes, exact int8 tensor-core group dots, fp32 fold" if args.w4a4_path == "int8" else
                       "int4 codes (one E4M3 byte each), exact fp32 tensor-core group dots, fp32 fold"),
             "data": "synthetic: W ~ N(0,0.02) rotated (H256) and quantised to int4 g64 on the device, "
                     "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
@@ -705,7 +706,7 @@ def run_block(args):
             "gpu_launches": timed_launches,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "roofline": {"kernel": "w4a4_pair::gemm_kernel" if wide_path else "w4a4::gemm_kernel", "bound": "tensor",
+            "roofline": {"kernel": "w4a4::gemm_kernel" if args.w4a4_path == "int8" else "w4a4_pair::gemm_kernel", "bound": "tensor",
                          "achieved": achieved, "peak": eight_bit_peak, "unit": "TOP/s", "frac": achieved / eight_bit_peak,
                          "frac_of_2x_bf16_burst": achieved / (2.0 * peaks["bf16_burst"]),
                          "frac_of_2x_bf16_sustained": achieved / (2.0 * peaks["bf16_sustained"]),
@@ -1214,9 +1215,10 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU and reference-kernel legs (profiling runs)")
     parser.add_argument("--no-other-kernels", action="store_true",
                         help="skip the W4A16 GEMM / GEMV / quantiser figures (profiling runs)")
-    parser.add_argument("--w4a4-path", default="wide", choices=["packed", "wide"],
-                        help="packed: the drop-in kernels on nibble-packed codes (int8 tensor-core dots); "
-                             "wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
+    parser.add_argument("--w4a4-path", default="wide", choices=["packed", "int8", "wide"],
+                        help="packed: the drop-in entry points on nibble-packed codes, kernel by shape (both operands widened into "
+                             "pool scratch for the CTA-pair kernel); int8: the same entry points held to the int8 kernel that widens "
+                             "the nibbles in shared memory; wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
     parser.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "slabs", "nccl"],
                         help="N > 1: how the column slices reach every GPU. nccl (auto): an all-gather after each GEMM; fused: the "
                              "GEMM's epilogue stores its slice into every GPU's output over NVLink, a barrier follows; copy: the copy "
