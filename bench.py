@@ -449,9 +449,11 @@ def run_block(args):
             full.append((w_codes, w_scales))  # kept until the gathered outputs have been checked
         del w_codes, w_scales
         layers.append(layer)
-    if args.gather == "auto":
-        args.gather = "nccl"
     wide_path = args.w4a4_path == "wide"
+    if args.gather == "auto":
+        # measured on the M = 4096 and M = 16384 blocks: on two GPUs the copy engines leave the GEMMs undisturbed
+        # (1213 against 1018 TOP/s, 1426 against 1082); from four GPUs on they do not keep up and NCCL's all-gather wins
+        args.gather = "copy" if world == 2 and wide_path else "nccl"
     fused = context is not None and args.gather == "fused" and wide_path
     # "copy": the GEMM writes its slice into this rank's whole output, then the copy engines carry it to the others
     # "slabs": the same with the whole output kept as slabs [ranks][rows][N/ranks], so that each copy is one contiguous block
@@ -1220,7 +1222,7 @@ def main():
                              "pool scratch for the CTA-pair kernel); int8: the same entry points held to the int8 kernel that widens "
                              "the nibbles in shared memory; wide: byte-wide E4M3 codes on CTA pairs (weights widened once at load)")
     parser.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "slabs", "nccl"],
-                        help="N > 1: how the column slices reach every GPU. nccl (auto): an all-gather after each GEMM; fused: the "
+                        help="N > 1: how the column slices reach every GPU. auto: copy on two GPUs, nccl on more. nccl: an all-gather after each GEMM; fused: the "
                              "GEMM's epilogue stores its slice into every GPU's output over NVLink, a barrier follows; copy: the copy "
                              "engines carry the slice to every GPU, a barrier follows; slabs: the same with outputs [ranks][rows][N/ranks]")
     parser.add_argument("--parallel", default="columns", choices=["columns", "pairs"],
