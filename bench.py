@@ -744,6 +744,8 @@ def run_block_pairs(args):
     context, stream, handle = job.context, job.stream, job.handle
     assert context is not None, "--parallel pairs is a multi-GPU mode"
     m = args.m
+    scatter = args.sum == "reduce-scatter"
+    assert m % world == 0, "rows must divide by the number of ranks"
     generator = torch.Generator(device=device)
     generator.manual_seed(1234)
     layers, full = [], []
@@ -776,7 +778,8 @@ def run_block_pairs(args):
             "a_scales": torch.empty(m, k_local // 64, dtype=torch.float16, device=device),
             "y_local": torch.empty(m, n_local, dtype=torch.float16, device=device) if split != "inputs" else None,
             "y_sum": torch.empty(m, n, dtype=torch.float32, device=device) if split == "inputs" else None,
-            "y_half": torch.empty(m, n, dtype=torch.float16, device=device) if split == "inputs" else None,
+            "y_half": torch.empty(m // world if scatter else m, n, dtype=torch.float16, device=device) if split == "inputs" else None,
+            "y_share": torch.empty(m // world, n, dtype=torch.float32, device=device) if split == "inputs" and scatter else None,
             "y_all": torch.empty(world, m, n_local, dtype=torch.float16, device=device) if split == "columns+gather" else None,
         })
         full.append((w_codes, w_scales, x))
@@ -813,9 +816,13 @@ def run_block_pairs(args):
             computed.record(stream)
             side.wait_event(computed)
             if layer["split"] == "inputs":
-                status = context.all_reduce(layer["y_sum"], m * layer["n"], side.cuda_stream)
                 y_half = layer["y_half"] if slot is None else layer["y_slots"][slot]
-                status = status or qi.f32_to_f16_ex(layer["y_sum"], y_half, m * layer["n"], side.cuda_stream)
+                if scatter:
+                    status = context.reduce_scatter(layer["y_sum"], layer["y_share"], (m // world) * layer["n"], side.cuda_stream)
+                    status = status or qi.f32_to_f16_ex(layer["y_share"], y_half, (m // world) * layer["n"], side.cuda_stream)
+                else:
+                    status = context.all_reduce(layer["y_sum"], m * layer["n"], side.cuda_stream)
+                    status = status or qi.f32_to_f16_ex(layer["y_sum"], y_half, m * layer["n"], side.cuda_stream)
                 launches["count"] += 1
             else:
                 status = context.all_gather(y_out, layer["y_all"], qi.DTYPE_F16, m, n_local, side.cuda_stream)
@@ -843,7 +850,9 @@ def run_block_pairs(args):
         assert qi.w4a4_gemm_wide_ex(a_wide, scales, w_wide, w_scales, None, expected, qi.DTYPE_F16, n, m, n, k, handle) == 0
         stream.synchronize()
         if layer["split"] == "inputs":
-            got, want = layer["y_half"].float(), expected.float()
+            share = m // world
+            got = layer["y_half"].float()
+            want = (expected[rank * share:(rank + 1) * share] if scatter else expected).float()
             error = float(((got - want).abs() / (want.abs() + 1e-3 * want.abs().max())).max())
             worst = max(worst, error)
             assert error <= 2e-3, f"{layer['name']}: the summed output is {error:.2e} away from the unsharded one on rank {rank}"
@@ -909,7 +918,7 @@ def run_block_pairs(args):
             with torch.cuda.stream(out_stream):
                 for layer, hy in zip(layers, host_y):
                     source = layer["y_slots"][slot]
-                    hy.copy_(source[rank * rows:(rank + 1) * rows] if layer["split"] == "inputs" else source, non_blocking=True)
+                    hy.copy_(source[rank * rows:(rank + 1) * rows] if layer["split"] == "inputs" and not scatter else source, non_blocking=True)
             copied_out[slot] = torch.cuda.Event()
             copied_out[slot].record(out_stream)
 
@@ -944,8 +953,9 @@ def run_block_pairs(args):
                     "X fp16 ~ N(0,1) with 1% outlier channels x20 (fc2 input: GELU-tanh of N(0,1)); seed 1234",
             "config": {"workload": workload_text(m), "name": args.workload, "m": m, "ops_per_step": ops_per_step,
                        "w4a4_path": "wide", "outputs": "fp16",
-                       "parallelism": f"paired splits x{world} ({splits}); float32 partial results summed by NCCL all-reduce on a "
-                                      "second stream, then stored as fp16; activation quantiser on each rank's own inputs",
+                       "parallelism": f"paired splits x{world} ({splits}); float32 partial results summed by NCCL "
+                                      + ("reduce-scatter (each rank keeps its share of the rows)" if scatter else "all-reduce")
+                                      + " on a second stream, then stored as fp16; activation quantiser on each rank's own inputs",
                        "l2": "per-step working set exceeds the 126 MB L2"},
             "gpu_launches": timed_launches,
             "e2e": {"value": ops_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
@@ -1229,6 +1239,10 @@ def main():
                         help="N > 1, block workloads: columns: every linear split by output columns and its slices gathered (the "
                              "default); pairs: qkv and fc1 by output columns without a gather, out and fc2 by input columns with an "
                              "all-reduce of the float32 partial results")
+    parser.add_argument("--sum", default="all-reduce", choices=["all-reduce", "reduce-scatter"],
+                        help="--parallel pairs: what becomes of the partial results of out and fc2. all-reduce: every GPU ends with the "
+                             "whole output (the operator's contract). reduce-scatter: GPU r ends with rows [r M / N, (r + 1) M / N) only - "
+                             "half the bytes - for a pipeline whose next kernels (layer norm, quantiser) work on rows")
     parser.add_argument("--shard-quantiser", action="store_true",
                         help="N > 1: every rank quantises its share of the rows and the codes and scales are all-gathered, "
                              "instead of every rank quantising all rows (measured slower on 2 GPUs: two more NCCL launches "

@@ -360,6 +360,12 @@ int qi_shard_plan_inputs(int k, int scheme, int ranks, int rank, int *first_inpu
  * run the partial product themselves (qi_w4a4_gemm_wide_ex and the like on an input slice, float32 output) and want
  * the sum on another stream, under the next linear's kernels. No counterpart in the reference (single GPU). */
 int qi_shard_all_reduce_f32(void *context, float *y, unsigned long long count, void *stream);
+/* Half of that sum: y [ranks * count_per_rank] float32 on every rank -> y_share [count_per_rank] on rank r = the sum
+ * over ranks of y[r * count_per_rank ...] (ncclReduceScatter). For a caller whose next step works on rows - a
+ * layer norm, the activation quantiser - and so wants rank r to end with rows [r * rows / R, (r + 1) * rows / R) of a
+ * row-parallel linear's output only: half the bytes of the all-reduce cross NVLink. No counterpart in the reference. */
+int qi_shard_reduce_scatter_f32(void *context, const float *y, float *y_share, unsigned long long count_per_rank,
+                                void *stream);
 int qi_shard_linear_inputs(void *context, const struct qi_packed_linear *local_record, const struct qi_linear_work *work,
                            const void *input_local, int input_dtype, float *y, int rows, int reuse_input, void *stream);
 

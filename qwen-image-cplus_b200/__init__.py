@@ -120,6 +120,7 @@ SIGNATURES = {
     "qi_shard_rank": [_P, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
     "qi_shard_all_gather": [_P, _P, _P, _I, _I, _I, _P],
     "qi_shard_all_reduce_f32": [_P, _P, ctypes.c_ulonglong, _P],
+    "qi_shard_reduce_scatter_f32": [_P, _P, _P, ctypes.c_ulonglong, _P],
     "qi_shard_barrier": [_P, _P],
     "qi_shard_put_slice": [_P, ctypes.POINTER(ctypes.c_void_p), _I, _I, _LL, _I, _I, _I, _P],
     "qi_shard_peer_export": [_P, _P, ctypes.POINTER(ctypes.c_size_t)],
@@ -511,6 +512,10 @@ class ShardContext:
     def all_reduce(self, y, count: int, stream=None) -> int:
         """y [count] float32 <- the sum over the ranks, in place."""
         return lib().qi_shard_all_reduce_f32(self.handle, _p(y), count, _p(stream))
+
+    def reduce_scatter(self, y, y_share, count_per_rank: int, stream=None) -> int:
+        """y_share [count_per_rank] float32 <- this rank's part of the sum over the ranks of y [ranks * count_per_rank]."""
+        return lib().qi_shard_reduce_scatter_f32(self.handle, _p(y), _p(y_share), count_per_rank, _p(stream))
 
     def put_slice(self, copies, output_dtype: int, ldy: int, column: int, rows: int, n_local: int, stream=None) -> int:
         return lib().qi_shard_put_slice(self.handle, copies, len(copies), output_dtype, ldy, column, rows, n_local,

@@ -39,6 +39,7 @@ struct Nccl {
     int (*CommAbort)(void *) = nullptr;
     int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
     int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*ReduceScatter)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
     bool ok() const { return handle && GetUniqueId && CommInitRank && CommDestroy && AllGather; }
 };
 
@@ -60,6 +61,7 @@ inline Nccl &nccl() {
             api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(api.handle, "ncclCommAbort"));
             api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
             api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
+            api.ReduceScatter = reinterpret_cast<decltype(api.ReduceScatter)>(dlsym(api.handle, "ncclReduceScatter"));
         }
     });
     return api;
@@ -238,6 +240,19 @@ int qi_shard_all_reduce_f32(void *context, float *y, unsigned long long count, v
     if (nccl().AllReduce == nullptr) return NCCL_MISSING;
     const int result = nccl().AllReduce(y, y, static_cast<size_t>(count), NCCL_FLOAT32, 0 /* ncclSum */, c->comm,
                                         static_cast<cudaStream_t>(stream));
+    return result == 0 ? 0 : NCCL_ERROR_BASE + result;
+}
+
+int qi_shard_reduce_scatter_f32(void *context, const float *y, float *y_share, unsigned long long count_per_rank, void *stream) {
+    using namespace qi::shard;
+    Context *c = checked(context);
+    if (c == nullptr || y == nullptr || y_share == nullptr || count_per_rank == 0) return static_cast<int>(cudaErrorInvalidValue);
+    if (c->ranks == 1)
+        return static_cast<int>(cudaMemcpyAsync(y_share, y, count_per_rank * sizeof(float), cudaMemcpyDeviceToDevice,
+                                                static_cast<cudaStream_t>(stream)));
+    if (nccl().ReduceScatter == nullptr) return NCCL_MISSING;
+    const int result = nccl().ReduceScatter(y, y_share, static_cast<size_t>(count_per_rank), NCCL_FLOAT32, 0 /* ncclSum */, c->comm,
+                                            static_cast<cudaStream_t>(stream));
     return result == 0 ? 0 : NCCL_ERROR_BASE + result;
 }
 

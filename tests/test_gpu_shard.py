@@ -147,6 +147,13 @@ def _worker(rank, ranks, port, result_path):
     assert context.all_reduce(part, part.numel()) == 0
     torch.cuda.synchronize()
     ok = ok and bool((part == float(sum(range(1, ranks + 1)))).all())
+    # and half of it: rank r keeps the r-th part of the sum
+    whole = torch.arange(ranks * 500, dtype=torch.float32, device=device) * float(rank + 1)
+    share = torch.full((500,), float("nan"), dtype=torch.float32, device=device)
+    assert context.reduce_scatter(whole, share, 500) == 0
+    torch.cuda.synchronize()
+    expected_share = torch.arange(rank * 500, (rank + 1) * 500, dtype=torch.float32, device=device) * float(sum(range(1, ranks + 1)))
+    ok = ok and bool((share == expected_share).all())
     assert context.destroy() == 0
     dist.barrier()
     if rank == 0:

@@ -89,6 +89,7 @@ def test_placing_entry_points_reject_illegal_arguments_before_any_cuda_call(qi):
     assert lib.qi_shard_put_slice(None, copies, 2, qi.DTYPE_F16, 512, 0, 128, 256, None) == invalid
     assert lib.qi_shard_barrier(None, None) == invalid
     assert lib.qi_shard_all_reduce_f32(None, fake, 16, None) == invalid
+    assert lib.qi_shard_reduce_scatter_f32(None, fake, fake, 16, None) == invalid
     offset = ctypes.c_size_t(0)
     assert lib.qi_shard_peer_export(None, ctypes.create_string_buffer(64), ctypes.byref(offset)) == invalid
     pointer = ctypes.c_void_p(0)
