@@ -450,6 +450,7 @@ def run_block(args):
         del w_codes, w_scales
         layers.append(layer)
     wide_path = args.w4a4_path == "wide"
+    gather_by_default = args.gather == "auto"
     if args.gather == "auto":
         # measured on the M = 4096 and M = 16384 blocks: on two GPUs the copy engines leave the GEMMs undisturbed
         # (1213 against 1018 TOP/s, 1426 against 1082); from four GPUs on they do not keep up and NCCL's all-gather wins
@@ -473,7 +474,15 @@ def run_block(args):
             dist.all_gather_object(items, item)
             return items
 
-        peers = qi.PeerOutput(context, pool, exchange)
+        try:
+            peers = qi.PeerOutput(context, pool, exchange)
+        except qi.PeerMappingError:
+            if not gather_by_default:
+                raise
+            peers = None  # every rank gets here together: the ranks may not share memory on this box
+            del pool
+            args.gather, fused, slabs, copied, placed = "nccl", False, False, False, False
+    if placed:
         offset = 0
         for layer, size in zip(layers, sizes):
             layer["whole"], layer["copies"], layer["mine"] = [], [], []

@@ -548,6 +548,10 @@ class ShardContext:
 SHARD_PEER_HANDLE_BYTES = 64
 
 
+class PeerMappingError(RuntimeError):
+    """The ranks cannot map each other's device memory (qi_shard_peer_export / qi_shard_peer_open refused)."""
+
+
 class PeerOutput:
     """The same device buffer on every rank of the box, each rank holding addresses of all copies.
 
@@ -556,27 +560,34 @@ class PeerOutput:
     all ranks' items in rank order (torch.distributed.all_gather_object, for instance). Collective."""
 
     def __init__(self, context: ShardContext, local, exchange):
+        """Raises PeerMappingError on EVERY rank when any rank could not export or map a buffer (a box whose
+        processes may not share device memory): a rank never leaves the others waiting in `exchange`."""
         handle = ctypes.create_string_buffer(SHARD_PEER_HANDLE_BYTES)
         offset = ctypes.c_size_t(0)
-        status = lib().qi_shard_peer_export(_p(local), handle, ctypes.byref(offset))
-        if status != 0:
-            raise RuntimeError(f"qi_shard_peer_export: status {status}")
-        everyone = exchange((handle.raw, offset.value))
+        exported = lib().qi_shard_peer_export(_p(local), handle, ctypes.byref(offset))
+        everyone = exchange((exported, handle.raw, offset.value))
         if len(everyone) != context.ranks:
             raise RuntimeError("exchange() must return one item per rank")
         self.rank, self.ranks = context.rank, context.ranks
         self.addresses, self._opened = [], []
-        for rank, (raw, peer_offset) in enumerate(everyone):
-            if rank == context.rank:
-                self.addresses.append(_p(local).value)
-                continue
-            pointer = ctypes.c_void_p(0)
-            status = lib().qi_shard_peer_open(ctypes.create_string_buffer(raw, SHARD_PEER_HANDLE_BYTES), peer_offset,
-                                              ctypes.byref(pointer))
-            if status != 0:
-                raise RuntimeError(f"qi_shard_peer_open (rank {rank}): status {status}")
-            self.addresses.append(pointer.value)
-            self._opened.append((pointer.value, peer_offset))
+        opened = 0
+        if all(status == 0 for status, _, _ in everyone):
+            for rank, (_, raw, peer_offset) in enumerate(everyone):
+                if rank == context.rank:
+                    self.addresses.append(_p(local).value)
+                    continue
+                pointer = ctypes.c_void_p(0)
+                opened = lib().qi_shard_peer_open(ctypes.create_string_buffer(raw, SHARD_PEER_HANDLE_BYTES), peer_offset,
+                                                  ctypes.byref(pointer))
+                if opened != 0:
+                    break
+                self.addresses.append(pointer.value)
+                self._opened.append((pointer.value, peer_offset))
+        outcomes = exchange(opened)  # every rank learns whether every rank has every mapping
+        failed = [status for status, _, _ in everyone if status != 0] + [status for status in outcomes if status != 0]
+        if failed:
+            self.close()
+            raise PeerMappingError(f"a buffer could not be shared between the ranks (first status {failed[0]})")
 
     def copies(self, byte_offset: int = 0):
         """A C array of every rank's address of the byte `byte_offset` of the buffer."""
